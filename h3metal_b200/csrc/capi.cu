@@ -1,0 +1,390 @@
+// C ABI of libh3b200 (include/h3b200.h): context, error reporting, stream/timing/profiling, argument checks and
+// TMA descriptor construction around the two kernels. Mirrors the conventions of the reference's Metal launcher
+// (src/capi.mm of audenvenn/h3metal): thread-local error string, NULL / non-zero on failure, ordered asynchronous
+// launches, a blocking wait that reports GPU time, and a per-launch profile mode.
+#include "../../include/h3b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "kernels.h"
+
+namespace {
+
+thread_local std::string g_error;
+
+int fail(const std::string &msg) {
+  g_error = msg;
+  return -1;
+}
+int fail_cuda(const char *what, cudaError_t e) {
+  return fail(std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct MapKey {
+  const void *ptr;
+  uint64_t inner, rows, stride_bytes;
+  uint32_t box_inner, box_rows;
+  int dtype, swizzle;
+  bool operator==(const MapKey &o) const {
+    return ptr == o.ptr && inner == o.inner && rows == o.rows && stride_bytes == o.stride_bytes &&
+           box_inner == o.box_inner && box_rows == o.box_rows && dtype == o.dtype && swizzle == o.swizzle;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey &k) const {
+    uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+    for (uint64_t v : {k.inner, k.rows, k.stride_bytes, static_cast<uint64_t>(k.box_inner),
+                       static_cast<uint64_t>(k.box_rows), static_cast<uint64_t>(k.dtype),
+                       static_cast<uint64_t>(k.swizzle)})
+      h = (h ^ v) * 0x100000001B3ull;
+    return static_cast<size_t>(h);
+  }
+};
+
+const char *status_text(int code) {
+  switch (code) {
+    case 1: return "TMA producer timed out waiting for a free shared-memory stage";
+    case 2: return "MMA issuer timed out waiting for operands or a free accumulator";
+    case 3: return "epilogue timed out waiting for an accumulator";
+    case 4: return "wind-down timed out waiting for copies in flight";
+    default: return "unknown device status";
+  }
+}
+
+}  // namespace
+
+struct h3b_ctx {
+  int device = 0;
+  cudaDeviceProp prop{};
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev_start = nullptr, ev_end = nullptr;
+  bool timing_open = false;
+  bool profile = false;
+  std::vector<double> prof;
+  int *status_dev = nullptr;   // device word the kernels write on a bounded-wait timeout
+  int *status_host = nullptr;  // pinned copy read at wait
+  EncodeTiledFn encode = nullptr;
+  std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
+  int tile_n_override = 0, band_override = 0, rot_threads = 0;
+  uint64_t launches = 0;
+  std::string name;
+
+  int make_current() {
+    cudaError_t e = cudaSetDevice(device);
+    return e == cudaSuccess ? 0 : fail_cuda("cudaSetDevice", e);
+  }
+  // Called before every launch: opens the timed region of the next wait.
+  int before_launch(cudaEvent_t *prof_start) {
+    if (make_current()) return -1;
+    cudaError_t e;
+    if (profile) {
+      if ((e = cudaEventRecord(ev_start, stream)) != cudaSuccess) return fail_cuda("cudaEventRecord", e);
+      *prof_start = ev_start;
+    } else if (!timing_open) {
+      if ((e = cudaEventRecord(ev_start, stream)) != cudaSuccess) return fail_cuda("cudaEventRecord", e);
+      timing_open = true;
+    }
+    return 0;
+  }
+  int after_launch(const char *what, cudaError_t launch_err) {
+    if (launch_err != cudaSuccess) return fail_cuda(what, launch_err);
+    ++launches;
+    if (profile) {
+      cudaError_t e;
+      if ((e = cudaEventRecord(ev_end, stream)) != cudaSuccess) return fail_cuda("cudaEventRecord", e);
+      if ((e = cudaEventSynchronize(ev_end)) != cudaSuccess) return fail_cuda(what, e);
+      float ms = 0;
+      if ((e = cudaEventElapsedTime(&ms, ev_start, ev_end)) != cudaSuccess) return fail_cuda("cudaEventElapsedTime", e);
+      prof.push_back(ms * 1e-3);
+    }
+    return 0;
+  }
+  const CUtensorMap *tensor_map(const void *ptr, int dtype, uint64_t inner, uint64_t rows, uint64_t stride_bytes,
+                                uint32_t box_inner, uint32_t box_rows, int swizzle) {
+    const MapKey key{ptr, inner, rows, stride_bytes, box_inner, box_rows, dtype, swizzle};
+    auto it = maps.find(key);
+    if (it != maps.end()) return &it->second;
+    CUtensorMap m;
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = dtype == h3b::kDtypeF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const CUtensorMapSwizzle sw = swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    const CUresult r = encode(&m, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      char buf[256];
+      snprintf(buf, sizeof buf,
+               "cuTensorMapEncodeTiled failed (%d) for ptr %p inner %llu rows %llu stride %llu box %u x %u", (int)r, ptr,
+               (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)stride_bytes, box_inner, box_rows);
+      fail(buf);
+      return nullptr;
+    }
+    if (maps.size() > 4096) maps.clear();  // bound the cache; descriptors are cheap to rebuild
+    return &maps.emplace(key, m).first->second;
+  }
+};
+
+extern "C" {
+
+const char *h3b_last_error(void) { return g_error.c_str(); }
+
+h3b_ctx *h3b_open(int device) {
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess) {
+    fail_cuda("cudaGetDeviceCount", e);
+    return nullptr;
+  }
+  if (device < 0 || device >= count) {
+    fail("device " + std::to_string(device) + " does not exist (" + std::to_string(count) + " CUDA devices)");
+    return nullptr;
+  }
+  h3b_ctx *ctx = new h3b_ctx;
+  ctx->device = device;
+  auto bail = [&](const char *what, cudaError_t err) -> h3b_ctx * {
+    fail_cuda(what, err);
+    delete ctx;
+    return nullptr;
+  };
+  if ((e = cudaSetDevice(device)) != cudaSuccess) return bail("cudaSetDevice", e);
+  if ((e = cudaGetDeviceProperties(&ctx->prop, device)) != cudaSuccess) return bail("cudaGetDeviceProperties", e);
+  if (ctx->prop.major != 10 || ctx->prop.minor != 0) {
+    fail(std::string("device ") + ctx->prop.name + " is compute capability " + std::to_string(ctx->prop.major) + "." +
+         std::to_string(ctx->prop.minor) + "; this library is built for 10.0 (sm_100a: tcgen05 kind::i8) only");
+    delete ctx;
+    return nullptr;
+  }
+  ctx->name = ctx->prop.name;
+  if ((e = cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking)) != cudaSuccess)
+    return bail("cudaStreamCreate", e);
+  ctx->stream = ctx->own_stream;
+  if ((e = cudaEventCreate(&ctx->ev_start)) != cudaSuccess) return bail("cudaEventCreate", e);
+  if ((e = cudaEventCreate(&ctx->ev_end)) != cudaSuccess) return bail("cudaEventCreate", e);
+  if ((e = cudaMalloc(&ctx->status_dev, sizeof(int))) != cudaSuccess) return bail("cudaMalloc", e);
+  if ((e = cudaMemset(ctx->status_dev, 0, sizeof(int))) != cudaSuccess) return bail("cudaMemset", e);
+  if ((e = cudaMallocHost(&ctx->status_host, sizeof(int))) != cudaSuccess) return bail("cudaMallocHost", e);
+  *ctx->status_host = 0;
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if ((e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q)) != cudaSuccess || !fn ||
+      q != cudaDriverEntryPointSuccess) {
+    if (e == cudaSuccess) e = cudaErrorUnknown;
+    return bail("cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)", e);
+  }
+  ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  if ((e = h3b::gemm_configure(device)) != cudaSuccess) return bail("cudaFuncSetAttribute(max dynamic shared memory)", e);
+  return ctx;
+}
+
+void h3b_close(h3b_ctx *ctx) {
+  if (!ctx) return;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
+  if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
+  if (ctx->ev_end) cudaEventDestroy(ctx->ev_end);
+  if (ctx->status_dev) cudaFree(ctx->status_dev);
+  if (ctx->status_host) cudaFreeHost(ctx->status_host);
+  if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+  delete ctx;
+}
+
+const char *h3b_device_name(h3b_ctx *ctx) { return ctx ? ctx->name.c_str() : ""; }
+uint64_t h3b_recommended_working_set(h3b_ctx *ctx) { return ctx ? ctx->prop.totalGlobalMem : 0; }
+uint64_t h3b_max_buffer_length(h3b_ctx *ctx) { return ctx ? ctx->prop.totalGlobalMem : 0; }
+int h3b_sm_count(h3b_ctx *ctx) { return ctx ? ctx->prop.multiProcessorCount : 0; }
+
+int h3b_set_stream(h3b_ctx *ctx, void *cuda_stream) {
+  if (!ctx) return fail("null context");
+  ctx->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
+  return 0;
+}
+
+int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target) {
+  if (!ctx) return fail("null context");
+  ctx->rot_threads = threads_target;
+  return 0;
+}
+
+int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, float *sa, int M, int D,
+               int block, int mode, int out_hr) {
+  if (!ctx) return fail("null context");
+  if (!x || !out || (!out_hr && !sa)) return fail("rot_q8: null tensor argument");
+  if (M <= 0 || D <= 0) return fail("rot_q8: M and D must be positive");
+  if (block != 64 && block != 128 && block != 256) return fail("rot_q8: rotation block must be 64, 128 or 256");
+  if (D % block) return fail("rot_q8: D " + std::to_string(D) + " is not a multiple of the rotation block " + std::to_string(block));
+  if (mode != 0 && mode != 1) return fail("rot_q8: mode must be 0 or 1");
+  const int esize = x_dtype == H3B_F32 ? 4 : (x_dtype == H3B_F16 || x_dtype == H3B_BF16) ? 2 : 0;
+  if (!esize) return fail("rot_q8: input type must be bf16, f16 or f32");
+  if (x_stride < (mode == 1 ? 2LL * D : D)) return fail("rot_q8: x_stride is smaller than the row");
+  if (reinterpret_cast<uintptr_t>(x) % 16 || (x_stride * esize) % 16)
+    return fail("rot_q8: input rows must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(out) % 16) return fail("rot_q8: output must be 16-byte aligned");
+  int target = ctx->rot_threads > 0 ? ctx->rot_threads : 512;
+  if (target < 32) target = 32;
+  if (target > 512) target = 512;
+  int ch, threads;
+  h3b::rot_q8_geometry(D, target, &ch, &threads);
+  if (threads > 1024) return fail("rot_q8: D " + std::to_string(D) + " exceeds the 65536 channels one CTA covers");
+  cudaEvent_t ps = nullptr;
+  if (ctx->before_launch(&ps)) return -1;
+  const cudaError_t e = h3b::launch_rot_q8(x, x_dtype, x_stride, out, sa, M, D, block, mode, out_hr, target, ctx->stream);
+  return ctx->after_launch("rot_q8 launch", e);
+}
+
+int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band) {
+  if (!ctx) return fail("null context");
+  if (tile_n != 0 && tile_n != 32 && tile_n != 64 && tile_n != 128 && tile_n != 256)
+    return fail("gemm policy: tile_n must be 0, 32, 64, 128 or 256");
+  if (band < 0) return fail("gemm policy: band must be >= 0");
+  ctx->tile_n_override = tile_n;
+  ctx->band_override = band;
+  return 0;
+}
+
+int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int /*lora*/) {
+  if (ctx && ctx->tile_n_override) return ctx->tile_n_override;
+  if (N <= 32) return 32;
+  if (N <= 64) return 64;
+  if (N <= 128) return 128;
+  if (N % 256 == 0 || N >= 2048) return 256;
+  return 128;
+}
+
+int h3b_gemm_w8a8(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
+                  const float *sw, const float *sa, const float *bias, void *C, int c_dtype, int64_t c_stride,
+                  int M, int N, int K, const void *lora_T, int64_t t_stride, const void *lora_B, int64_t b_stride,
+                  int R, const int32_t *lora_ranges) {
+  if (!ctx) return fail("null context");
+  if (!A || !W || !C) return fail("gemm: null tensor argument");
+  if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: M, N and K must be positive");
+  const bool raw = c_dtype == H3B_I32;
+  if (!raw && c_dtype != H3B_BF16 && c_dtype != H3B_F16 && c_dtype != H3B_F32)
+    return fail("gemm: output type must be bf16, f16, f32 or i32");
+  if (!raw && (!sw || !sa)) return fail("gemm: int8 products need row scales (sa) and column scales (sw)");
+  if (a_stride < K || w_stride < K) return fail("gemm: a_stride / w_stride smaller than K");
+  if (c_stride < N) return fail("gemm: c_stride smaller than N");
+  if (reinterpret_cast<uintptr_t>(A) % 16 || reinterpret_cast<uintptr_t>(W) % 16 || a_stride % 16 || w_stride % 16)
+    return fail("gemm: A and W must be 16-byte aligned with row strides that are multiples of 16 bytes");
+  const bool lora = !raw && lora_T != nullptr;
+  if (lora) {
+    if (!lora_B) return fail("gemm: low-rank term needs both T and B");
+    if (R <= 0 || R % 32 || R > 128) return fail("gemm: low-rank R must be a multiple of 32, at most 128");
+    if (t_stride < R || b_stride < R) return fail("gemm: t_stride / b_stride smaller than R");
+    if (reinterpret_cast<uintptr_t>(lora_T) % 16 || reinterpret_cast<uintptr_t>(lora_B) % 16 || (t_stride * 2) % 16 ||
+        (b_stride * 2) % 16)
+      return fail("gemm: T and B must be 16-byte aligned with row strides that are multiples of 16 bytes");
+  }
+  const int bn = h3b_gemm_tile_n(ctx, N, lora);
+  const int stages = h3b::gemm_pick_stages(bn, lora ? R : 0, ctx->prop.sharedMemPerBlockOptin);
+  if (stages < 2) return fail("gemm: tile does not fit the device's shared memory");
+
+  h3b::GemmLaunch g;
+  memset(&g, 0, sizeof g);
+  const CUtensorMap *m;
+  if (!(m = ctx->tensor_map(A, h3b::kDtypeI8, K, M, a_stride, 128, 128, 128))) return -1;
+  g.map_a = *m;
+  if (!(m = ctx->tensor_map(W, h3b::kDtypeI8, K, N, w_stride, 128, bn, 128))) return -1;
+  g.map_w = *m;
+  if (lora) {
+    if (!(m = ctx->tensor_map(lora_T, h3b::kDtypeF16, R, M, t_stride * 2, 32, 128, 64))) return -1;
+    g.map_t = *m;
+    if (!(m = ctx->tensor_map(lora_B, h3b::kDtypeF16, R, N, b_stride * 2, 32, bn, 64))) return -1;
+    g.map_b = *m;
+  }
+  g.sw = sw; g.sa = sa; g.bias = raw ? nullptr : bias; g.c = C; g.ranges = lora ? lora_ranges : nullptr;
+  g.c_stride = c_stride; g.c_dtype = c_dtype; g.M = M; g.N = N; g.K = K; g.R = lora ? R : 0; g.bn = bn;
+  g.acc_stages = (lora && bn == 256) ? 1 : 2;
+  const int m_tiles = (M + 127) / 128, n_tiles = (N + bn - 1) / bn;
+  int band = ctx->band_override;
+  if (band <= 0) {
+    // keep the A band (band x 128 rows x K bytes) well inside L2 while W streams through once per band
+    const long long budget = 24LL << 20;
+    band = static_cast<int>(budget / (128LL * K));
+    if (band < 4) band = 4;
+  }
+  if (band > m_tiles) band = m_tiles;
+  g.band = band;
+  const long long tiles = static_cast<long long>(m_tiles) * n_tiles;
+  g.grid = static_cast<int>(tiles < ctx->prop.multiProcessorCount ? tiles : ctx->prop.multiProcessorCount);
+  g.status = ctx->status_dev;
+
+  cudaEvent_t ps = nullptr;
+  if (ctx->before_launch(&ps)) return -1;
+  const cudaError_t e = h3b::launch_gemm_w8a8(g, stages, ctx->stream);
+  return ctx->after_launch("gemm launch", e);
+}
+
+void h3b_commit(h3b_ctx *) {}
+
+double h3b_wait(h3b_ctx *ctx) {
+  if (!ctx) {
+    fail("null context");
+    return -1.0;
+  }
+  if (ctx->make_current()) return -1.0;
+  cudaError_t e;
+  double seconds = 0.0;
+  if ((e = cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream)) != cudaSuccess) {
+    fail_cuda("status read", e);
+    return -1.0;
+  }
+  if (ctx->timing_open) {
+    if ((e = cudaEventRecord(ctx->ev_end, ctx->stream)) != cudaSuccess) {
+      fail_cuda("cudaEventRecord", e);
+      return -1.0;
+    }
+  }
+  if ((e = cudaStreamSynchronize(ctx->stream)) != cudaSuccess) {
+    ctx->timing_open = false;
+    fail_cuda("GPU work failed", e);
+    return -1.0;
+  }
+  if (ctx->timing_open) {
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, ctx->ev_start, ctx->ev_end) == cudaSuccess) seconds = ms * 1e-3;
+    ctx->timing_open = false;
+  }
+  if (*ctx->status_host != 0) {
+    const int code = *ctx->status_host;
+    *ctx->status_host = 0;
+    cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    fail(std::string("GPU kernel gave up: ") + status_text(code));
+    return -1.0;
+  }
+  return seconds;
+}
+
+void h3b_set_profile(h3b_ctx *ctx, int on) {
+  if (!ctx) return;
+  h3b_wait(ctx);
+  ctx->profile = on != 0;
+  ctx->prof.clear();
+}
+
+int h3b_profile_take(h3b_ctx *ctx, double *seconds, int max) {
+  if (!ctx || !seconds || max <= 0) return 0;
+  const int n = static_cast<int>(ctx->prof.size()) < max ? static_cast<int>(ctx->prof.size()) : max;
+  for (int i = 0; i < n; ++i) seconds[i] = ctx->prof[i];
+  ctx->prof.erase(ctx->prof.begin(), ctx->prof.begin() + n);
+  return n;
+}
+
+uint64_t h3b_launch_count(h3b_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+}  // extern "C"

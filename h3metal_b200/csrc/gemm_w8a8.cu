@@ -1,0 +1,425 @@
+// W8A8 product with fused dequantising epilogue:  C[m][n] = OUT_T(float(acc) * sa[m] * sw[n] + bias[n] + low[m][n])
+// with acc[m][n] = sum_k A[m][k] * W[n][k] exact in int32 and, optionally, low = T B'^T the rank-R LoRA term.
+//
+// This replaces the Q8 path of the reference's Metal kernel `gemm` (kernels/gemm.metal:117-153,201-260; weight
+// format 1, epilogue 0, low-rank term :211-229). A is int8 [M][K] and W int8 [N][K], both K-contiguous, so the
+// product is A W^T with both operands K-major. The epilogue keeps the reference's operation order in fp32:
+// convert the int32 accumulator (rounds above 2^24), multiply by the row scale, multiply by the column scale, add
+// the bias, add the low-rank term, convert to the output type.
+//
+// Blackwell mapping (sm_100a, one CTA per SM, persistent over output tiles of 128 x BN):
+//   warp 0  TMA producer: one thread issues cp.async.bulk.tensor loads of the A tile (128 rows x 128 bytes of K)
+//           and the W tile (BN rows x 128 bytes) into a ring of 128-byte-swizzled shared-memory stages, each
+//           guarded by a full/empty mbarrier pair. Rows or K beyond the tensor are zero-filled by TMA.
+//   warp 1  MMA issuer: one thread issues tcgen05.mma kind::i8 (M 128, N BN, K 32 per instruction, four per
+//           stage) accumulating int32 in tensor memory; tcgen05.commit releases the stage to the producer and,
+//           after the last K block, hands the accumulator to the epilogue. With a LoRA term the same thread first
+//           issues kind::f16 MMAs (fp16 x fp16 -> fp32) of the tile's T and B' slices into a second TMEM region.
+//   warps 2-5  epilogue: each warp owns 32 accumulator rows (its TMEM lane quarter), reads 32 columns at a time
+//           with tcgen05.ld, applies scales, bias and the low-rank term and stores 64-byte row segments.
+// Accumulators are double-buffered in TMEM (2 x BN columns of the 512) so the epilogue of one tile overlaps the
+// main loop of the next. Tiles are visited in bands of `band` row tiles per column tile so that the A band stays
+// in L2 while W streams through once per band.
+//
+// Every mbarrier wait is bounded (ptx.cuh): on a timeout the CTA sets the context's status word, stops taking
+// tiles, waits for its own TMA copies, frees its tensor memory and returns.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace h3b {
+namespace {
+
+constexpr int kBM = 128;            // rows per tile = MMA M
+constexpr int kBKBytes = 128;       // K bytes per stage row = one 128-byte swizzle span
+constexpr int kABytes = kBM * kBKBytes;
+constexpr int kMaxStages = 8;
+constexpr int kLoraChunk = 32;      // ranks per LoRA shared-memory chunk: 32 halves = one 64-byte swizzle span
+constexpr int kLoraTBytes = kBM * kLoraChunk * 2;
+constexpr int kTmemCols = 512;
+constexpr int kLowBase = 256;       // first TMEM column of the LoRA accumulators
+constexpr int kThreads = 192;
+constexpr int kBarrierBytes = 256;
+
+__host__ __device__ constexpr int stage_bytes(int bn) { return kABytes + bn * kBKBytes; }
+__host__ __device__ constexpr int lora_bytes(int bn, int R) { return (R / kLoraChunk) * (kLoraTBytes + bn * kLoraChunk * 2); }
+
+struct TileCoord {
+  int m_blk, n_blk;
+};
+
+// Tile t of the persistent schedule: bands of `band` row tiles; inside a band row tiles vary fastest.
+__device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_tiles, int band) {
+  const int per_band = band * n_tiles;
+  const int b = t / per_band;
+  const int rows = min(band, m_tiles - b * band);
+  const int r = t - b * per_band;
+  TileCoord c;
+  c.m_blk = b * band + r % rows;
+  c.n_blk = r / rows;
+  return c;
+}
+
+template <typename OUT_T>
+__device__ __forceinline__ OUT_T to_out(float v);
+template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// 32 consecutive values of one row, converted to OUT_T and packed into 32-bit words (16 words for 2-byte types).
+template <typename OUT_T>
+struct Packed;
+template <>
+struct Packed<float> {
+  static constexpr int kWords = 32;
+  static __device__ __forceinline__ void pack(const float (&v)[32], uint32_t (&w)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(v[j]);
+  }
+};
+template <>
+struct Packed<__half> {
+  static constexpr int kWords = 16;
+  static __device__ __forceinline__ void pack(const float (&v)[32], uint32_t (&w)[32]) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+  }
+};
+template <>
+struct Packed<__nv_bfloat16> {
+  static constexpr int kWords = 16;
+  static __device__ __forceinline__ void pack(const float (&v)[32], uint32_t (&w)[32]) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+  }
+};
+
+// Stores 32 consecutive output values of one row; 16-byte vector stores when the segment is aligned and whole.
+template <typename OUT_T>
+__device__ __forceinline__ void store_segment(OUT_T *dst, const float (&v)[32], int n_valid, bool vec_ok) {
+  if (vec_ok && n_valid >= 32) {
+    uint32_t w[32];
+    Packed<OUT_T>::pack(v, w);
+#pragma unroll
+    for (int j = 0; j < Packed<OUT_T>::kWords / 4; ++j)
+      reinterpret_cast<uint4 *>(dst)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < n_valid) dst[j] = to_out<OUT_T>(v[j]);
+    }
+  }
+}
+
+template <int BN, int ACC_STAGES, bool LORA>
+__global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_constant__ GemmLaunch g,
+                                                                const int stages) {
+  static_assert(ACC_STAGES * BN <= (LORA ? kLowBase : kTmemCols), "accumulators do not fit tensor memory");
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - raw_addr);
+
+  constexpr uint32_t kWBytes = BN * kBKBytes;
+  constexpr uint32_t kStage = kABytes + kWBytes;
+  constexpr uint32_t kLoraBBytes = BN * kLoraChunk * 2;
+  const int chunks = LORA ? g.R / kLoraChunk : 0;
+  const uint32_t lora_t = base + stages * kStage;
+  const uint32_t lora_b = lora_t + chunks * kLoraTBytes;
+  const uint32_t bars_off = stages * kStage + chunks * (kLoraTBytes + kLoraBBytes);
+  const uint32_t bars = base + bars_off;
+  auto full_bar = [&](int i) { return bars + 8u * i; };
+  auto empty_bar = [&](int i) { return bars + 64u + 8u * i; };
+  auto acc_full_bar = [&](int i) { return bars + 128u + 8u * i; };
+  auto acc_empty_bar = [&](int i) { return bars + 144u + 8u * i; };
+  const uint32_t lora_full_bar = bars + 160u, lora_empty_bar = bars + 168u;
+  volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(base_ptr + bars_off + 176);
+  volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + bars_off + 180);
+  float *col_stage = reinterpret_cast<float *>(base_ptr + bars_off + kBarrierBytes);  // [4 warps][2][BN]: sw, bias
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (g.M + kBM - 1) / kBM, n_tiles = (g.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (g.K + kBKBytes - 1) / kBKBytes;
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_descriptor(&g.map_a);
+    tma_prefetch_descriptor(&g.map_w);
+    if (LORA) {
+      tma_prefetch_descriptor(&g.map_t);
+      tma_prefetch_descriptor(&g.map_b);
+    }
+    for (int i = 0; i < stages; ++i) {
+      mbar_init(full_bar(i), 1);
+      mbar_init(empty_bar(i), 1);
+    }
+    for (int i = 0; i < ACC_STAGES; ++i) {
+      mbar_init(acc_full_bar(i), 1);
+      mbar_init(acc_empty_bar(i), 4);  // one arrival per epilogue warp
+    }
+    mbar_init(lora_full_bar, 1);
+    mbar_init(lora_empty_bar, 1);
+    *cta_abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_holder)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, g.band);
+        const int m0 = tc.m_blk * kBM, n0 = tc.n_blk * BN;
+        if (LORA) {
+          ok = mbar_wait(lora_empty_bar, (lt & 1u) ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
+          if (!ok) break;
+          mbar_arrive_expect_tx(lora_full_bar, chunks * (kLoraTBytes + kLoraBBytes));
+          for (int c = 0; c < chunks; ++c) {
+            tma_load_2d(lora_t + c * kLoraTBytes, &g.map_t, lora_full_bar, c * kLoraChunk, m0);
+            tma_load_2d(lora_b + c * kLoraBBytes, &g.map_b, lora_full_bar, c * kLoraChunk, n0);
+          }
+          ++lt;
+        }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1u;
+          ok = mbar_wait(empty_bar(s), ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
+          if (!ok) break;
+          mbar_arrive_expect_tx(full_bar(s), kStage);
+          const uint32_t dst = base + s * kStage;
+          tma_load_2d(dst, &g.map_a, full_bar(s), kb * kBKBytes, m0);
+          tma_load_2d(dst + kABytes, &g.map_w, full_bar(s), kb * kBKBytes, n0);
+        }
+      }
+      if (*cta_abort) {
+        // wind-down: wait (bounded) for the copies this thread still has in flight
+        const uint32_t first = it > static_cast<uint32_t>(stages) ? it - stages : 0u;
+        for (uint32_t j = first; j < it; ++j) {
+          int dummy_abort = 0;
+          mbar_wait(full_bar(j % stages), (j / stages) & 1u, &dummy_abort, g.status, kStatusDrainTimeout,
+                    kDrainLimitCycles);
+        }
+        if (LORA && lt > 0) {
+          int dummy_abort = 0;
+          mbar_wait(lora_full_bar, (lt - 1) & 1u, &dummy_abort, g.status, kStatusDrainTimeout, kDrainLimitCycles);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_i8 = umma_instr_desc(2, 1, kBM, BN);   // s32 accumulate, s8 x s8
+      constexpr uint32_t idesc_f16 = umma_instr_desc(1, 0, kBM, BN);  // f32 accumulate, f16 x f16
+      uint32_t it = 0, at = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++at) {
+        const int as = at % ACC_STAGES;
+        const uint32_t aph = (at / ACC_STAGES) & 1u;
+        ok = mbar_wait(acc_empty_bar(as), aph ^ 1u, cta_abort, g.status, kStatusMmaTimeout);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_acc = tmem_base + as * BN;
+        if (LORA) {
+          const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, g.band);
+          int k0 = 0, k1 = g.R;
+          if (g.ranges != nullptr) {
+            k0 = g.ranges[2 * tc.n_blk];
+            k1 = g.ranges[2 * tc.n_blk + 1];
+          }
+          ok = mbar_wait(lora_full_bar, lt & 1u, cta_abort, g.status, kStatusMmaTimeout);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t d_low = tmem_base + kLowBase + as * BN;
+          for (int kk = k0; kk < k1; kk += 16) {  // one kind::f16 instruction covers 16 ranks = 32 bytes
+            const int c = kk / kLoraChunk;
+            const uint32_t koff = ((kk % kLoraChunk) * 2) >> 4;
+            const uint64_t td = umma_smem_desc(lora_t + c * kLoraTBytes, 512, 4) + koff;
+            const uint64_t bd = umma_smem_desc(lora_b + c * kLoraBBytes, 512, 4) + koff;
+            umma_f16(d_low, td, bd, idesc_f16, kk != k0 ? 1u : 0u);
+          }
+          umma_commit(lora_empty_bar);  // the LoRA tiles may be overwritten once these MMAs have read them
+          ++lt;
+        }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1u;
+          ok = mbar_wait(full_bar(s), ph, cta_abort, g.status, kStatusMmaTimeout);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = base + s * kStage;
+          const uint64_t ad = umma_smem_desc(a_addr, 1024, 2);
+          const uint64_t bd = umma_smem_desc(a_addr + kABytes, 1024, 2);
+#pragma unroll
+          for (int k = 0; k < kBKBytes / 32; ++k) {  // 32 int8 of K per instruction = 32 bytes = 2 descriptor units
+            umma_i8(d_acc, ad + 2u * k, bd + 2u * k, idesc_i8, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));
+        }
+        if (!ok) break;
+        umma_commit(acc_full_bar(as));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------------------------- epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes 32 * quarter .. + 31 are the ones this warp may read
+    const int row = quarter * 32 + lane;
+    const bool raw = g.c_dtype == kDtypeI32;
+    const size_t esize = (g.c_dtype == kDtypeF32 || raw) ? 4 : 2;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(g.c) % 16 == 0) && ((g.c_stride * esize) % 16 == 0);
+    uint32_t at = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++at) {
+      const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, g.band);
+      const int m0 = tc.m_blk * kBM, n0 = tc.n_blk * BN;
+      const int as = at % ACC_STAGES;
+      const uint32_t aph = (at / ACC_STAGES) & 1u;
+      // per-column scale and bias of this tile -> this warp's own slice of shared memory (no cross-warp barrier)
+      float *sw_s = col_stage + quarter * 2 * BN, *bias_s = sw_s + BN;
+      __syncwarp();
+      if (!raw) {
+        for (int j = lane; j < BN; j += 32) {
+          const int n = n0 + j;
+          sw_s[j] = n < g.N ? __ldg(g.sw + n) : 0.0f;
+          bias_s[j] = (g.bias != nullptr && n < g.N) ? __ldg(g.bias + n) : 0.0f;
+        }
+      }
+      __syncwarp();
+      const int m = m0 + row;
+      const float sa_m = (!raw && m < g.M) ? __ldg(g.sa + m) : 0.0f;
+      bool has_low = false;
+      if (LORA) {
+        int k0 = 0, k1 = g.R;
+        if (g.ranges != nullptr) {
+          k0 = g.ranges[2 * tc.n_blk];
+          k1 = g.ranges[2 * tc.n_blk + 1];
+        }
+        has_low = k1 > k0;
+      }
+      ok = mbar_wait(acc_full_bar(as), aph, cta_abort, g.status, kStatusEpilogueTimeout);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN;
+      const uint32_t t_low = t_acc + kLowBase;
+      const bool has_bias = g.bias != nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t acc[32];
+        uint32_t low[32];
+        tmem_ld_32x32b_x32(t_acc + c * 32, acc);
+        if (LORA && has_low) tmem_ld_32x32b_x32(t_low + c * 32, low);
+        tmem_ld_wait();
+        const int n = n0 + c * 32;
+        const int n_valid = g.N - n;
+        if (m < g.M && n_valid > 0) {
+          if (raw) {
+            int32_t *dst = static_cast<int32_t *>(g.c) + static_cast<size_t>(m) * g.c_stride + n;
+            if (vec_ok && n_valid >= 32) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<uint4 *>(dst)[j] = make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (j < n_valid) dst[j] = static_cast<int32_t>(acc[j]);
+              }
+            }
+          } else {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(acc[j])), sa_m), sw_s[c * 32 + j]);
+              if (has_bias) x = __fadd_rn(x, bias_s[c * 32 + j]);
+              if (LORA && has_low) x = __fadd_rn(x, __uint_as_float(low[j]));
+              v[j] = x;
+            }
+            const size_t off = static_cast<size_t>(m) * g.c_stride + n;
+            if (g.c_dtype == kDtypeBf16) store_segment(static_cast<__nv_bfloat16 *>(g.c) + off, v, n_valid, vec_ok);
+            else if (g.c_dtype == kDtypeF16) store_segment(static_cast<__half *>(g.c) + off, v, n_valid, vec_ok);
+            else store_segment(static_cast<float *>(g.c) + off, v, n_valid, vec_ok);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(as));
+    }
+  }
+
+  // ------------------------------------------------------------------------------------ wind-down
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int BN, int ACC_STAGES, bool LORA>
+cudaError_t launch_one(const GemmLaunch &g, int stages, cudaStream_t stream) {
+  const size_t smem = gemm_smem_bytes(BN, LORA ? g.R : 0, stages);
+  gemm_w8a8_kernel<BN, ACC_STAGES, LORA><<<g.grid, kThreads, smem, stream>>>(g, stages);
+  return cudaGetLastError();
+}
+
+template <int BN, int ACC_STAGES, bool LORA>
+cudaError_t configure_one() {
+  return cudaFuncSetAttribute(gemm_w8a8_kernel<BN, ACC_STAGES, LORA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              232448);
+}
+
+}  // namespace
+
+size_t gemm_smem_bytes(int bn, int R, int stages) {
+  if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return 0;
+  if (R % kLoraChunk) return 0;
+  return 1024 + static_cast<size_t>(stages) * stage_bytes(bn) + lora_bytes(bn, R) + kBarrierBytes +
+         8 * static_cast<size_t>(bn) * sizeof(float);
+}
+
+int gemm_pick_stages(int bn, int R, size_t smem_optin) {
+  for (int s = kMaxStages; s >= 2; --s) {
+    const size_t need = gemm_smem_bytes(bn, R, s);
+    if (need != 0 && need <= smem_optin) return s;
+  }
+  return 0;
+}
+
+cudaError_t gemm_configure(int /*device*/) {
+  cudaError_t e;
+#define H3B_CFG(BN, AS, L) \
+  if ((e = configure_one<BN, AS, L>()) != cudaSuccess) return e;
+  H3B_CFG(32, 2, false) H3B_CFG(64, 2, false) H3B_CFG(128, 2, false) H3B_CFG(256, 2, false)
+  H3B_CFG(32, 2, true) H3B_CFG(64, 2, true) H3B_CFG(128, 2, true) H3B_CFG(256, 1, true)
+#undef H3B_CFG
+  return cudaSuccess;
+}
+
+cudaError_t launch_gemm_w8a8(const GemmLaunch &g, int stages, cudaStream_t stream) {
+  const bool lora = g.R > 0;
+  switch (g.bn) {
+    case 32: return lora ? launch_one<32, 2, true>(g, stages, stream) : launch_one<32, 2, false>(g, stages, stream);
+    case 64: return lora ? launch_one<64, 2, true>(g, stages, stream) : launch_one<64, 2, false>(g, stages, stream);
+    case 128: return lora ? launch_one<128, 2, true>(g, stages, stream) : launch_one<128, 2, false>(g, stages, stream);
+    case 256: return lora ? launch_one<256, 1, true>(g, stages, stream) : launch_one<256, 2, false>(g, stages, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace h3b

@@ -1,0 +1,47 @@
+// Internal (C++) interface between the C ABI (capi.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace h3b {
+
+// Element types as the C ABI numbers them (include/h3b200.h).
+enum Dtype : int { kDtypeF32 = 0, kDtypeF16 = 1, kDtypeBf16 = 2, kDtypeI8 = 3, kDtypeI32 = 4 };
+
+void rot_q8_geometry(int D, int threads_target, int *ch, int *threads);
+cudaError_t launch_rot_q8(const void *x, int x_dtype, long long x_stride, void *out, float *sa, int M, int D,
+                          int block, int mode, int out_hr, int threads_target, cudaStream_t stream);
+
+// Everything one launch of the int8 product needs. Tensor maps are built by the caller (capi.cu) because they
+// need the driver entry point and are cached per context.
+struct GemmLaunch {
+  CUtensorMap map_a;   // int8 [M][K], box 128 x 128 (rows x bytes), 128-byte swizzle
+  CUtensorMap map_w;   // int8 [N][K], box BN x 128
+  CUtensorMap map_t;   // fp16 [M][R], box 128 x 32 halves, 64-byte swizzle (LoRA only)
+  CUtensorMap map_b;   // fp16 [N][R], box BN x 32 halves (LoRA only)
+  const float *sw;     // [N]
+  const float *sa;     // [M]
+  const float *bias;   // [N] or null
+  void *c;             // [M][c_stride] of c_dtype
+  const int *ranges;   // (k0, k1) per BN-wide column tile, or null for the whole rank range
+  long long c_stride;
+  int c_dtype;         // kDtypeBf16 / kDtypeF16 / kDtypeF32, or kDtypeI32 for the raw accumulators
+  int M, N, K;
+  int R;               // LoRA rank (multiple of 32), 0 = no low-rank term
+  int bn;              // tile width: 32, 64, 128 or 256
+  int acc_stages;      // accumulator buffers in tensor memory: 1 or 2
+  int band;            // row tiles swept per column tile before moving on (L2 reuse)
+  int grid;            // CTAs (persistent)
+  int *status;         // device status word of the context
+};
+
+// Shared memory a launch with this tile width and rank needs for `stages` operand stages; 0 if unsupported.
+size_t gemm_smem_bytes(int bn, int R, int stages);
+// Largest stage count (<= 8) that fits the device's opt-in shared memory, or 0.
+int gemm_pick_stages(int bn, int R, size_t smem_optin);
+cudaError_t gemm_configure(int device);  // raises the dynamic shared-memory limit of every instantiation
+cudaError_t launch_gemm_w8a8(const GemmLaunch &g, int stages, cudaStream_t stream);
+
+}  // namespace h3b

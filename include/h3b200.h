@@ -1,0 +1,118 @@
+/* libh3b200: C ABI of the B200 (sm_100a) implementation of h3metal's W8A8 Hadamard-rotated linear.
+ *
+ * It stands where the reference's Metal launcher stands (src/capi.h of audenvenn/h3metal): a small C library that
+ * a Python (ctypes) host drives. The reference's library is a generic kernel launcher for run-time compiled Metal
+ * shaders; here the two kernels of the quantised-linear path are compiled ahead of time for sm_100a and exposed
+ * as typed entry points, while the context / error / commit / wait / profile conventions are kept:
+ *
+ *   - pointer-returning calls return NULL on failure, int-returning calls return 0 on success (src/capi.h:59-63);
+ *   - the message of the last failed call on this thread is read with h3b_last_error() (src/capi.h:26-27);
+ *   - launches are asynchronous and ordered on the context's stream; results are valid after h3b_wait(), which
+ *     returns the GPU seconds of the work since the previous wait, or a negative value on failure
+ *     (src/capi.h:64-70);
+ *   - a context is not thread-safe: one context per host thread / rank.
+ *
+ * Memory stays with the caller: every tensor argument is a plain device pointer plus sizes and strides in
+ * ELEMENTS. Nothing in these signatures is a PyTorch type.
+ */
+#ifndef H3B200_H
+#define H3B200_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define H3B_API __attribute__((visibility("default")))
+#else
+#define H3B_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct h3b_ctx h3b_ctx;
+
+/* element types of tensor arguments */
+enum { H3B_F32 = 0, H3B_F16 = 1, H3B_BF16 = 2, H3B_I8 = 3, H3B_I32 = 4 };
+
+/* Message of the last failed call on this thread (empty if none). Replaces h3_last_error (src/capi.h:27). */
+H3B_API const char *h3b_last_error(void);
+
+/* Opens CUDA device `device`, which must be compute capability 10.0 (the int8 tensor-core instruction used here
+ * exists only there), creates the context's stream and raises the kernels' shared-memory limits.
+ * Replaces h3_open (src/capi.h:29), whose argument was the shader directory. NULL on failure. */
+H3B_API h3b_ctx *h3b_open(int device);
+/* Waits for the context's work, then frees it. Replaces h3_close (src/capi.h:30). */
+H3B_API void h3b_close(h3b_ctx *ctx);
+/* Replaces h3_device_name (src/capi.h:31). */
+H3B_API const char *h3b_device_name(h3b_ctx *ctx);
+/* Device memory a working set may use (total device memory) and the largest single allocation.
+ * Replace h3_recommended_working_set / h3_max_buffer_length (src/capi.h:32-33). */
+H3B_API uint64_t h3b_recommended_working_set(h3b_ctx *ctx);
+H3B_API uint64_t h3b_max_buffer_length(h3b_ctx *ctx);
+/* Number of SMs of the device (grid sizing of the persistent product kernel). No reference counterpart. */
+H3B_API int h3b_sm_count(h3b_ctx *ctx);
+
+/* Makes later launches go to `cuda_stream` (a cudaStream_t; NULL = the context's own stream), so that a host
+ * that owns the tensors can order the kernels with its other work. No reference counterpart (Metal command
+ * queues are owned by the reference's context, src/metal_rt.h:16-45). Returns 0. */
+H3B_API int h3b_set_stream(h3b_ctx *ctx, void *cuda_stream);
+
+/* Rotate + per-token int8 quantise. Replaces the dispatch of the Metal kernel rot_q8
+ * (kernels/ops.metal:274-334; parameter block RotQParams kernels/params.h:25-29; launcher h3metal/ops.py:214-222).
+ *   x        [M][x_stride] of x_dtype (H3B_BF16 / H3B_F16 / H3B_F32); with mode 1 columns D..2D-1 hold the gates
+ *   out      int8 [M][D] contiguous; with out_hr != 0, fp16 [M][D] (rotated rows, not quantised)
+ *   sa       fp32 [M] row scales (ignored with out_hr)
+ *   block    rotation block: 64, 128 or 256 (the reference kernel has 256); D % block == 0
+ *   mode     0: rotate x; 1: rotate x[:, :D] * silu(x[:, D:2D])
+ * x must be 16-byte aligned with x_stride * sizeof(x_dtype) a multiple of 16; out 16-byte aligned. */
+H3B_API int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, float *sa, int M, int D,
+               int block, int mode, int out_hr);
+
+/* int8 x int8 product with the dequantising epilogue. Replaces the dispatch of the Metal kernel gemm with weight
+ * format 1 and epilogue 0 (kernels/gemm.metal:117-261; parameter block GemmParams kernels/params.h:7-16; launcher
+ * h3metal/ops.py:124-174; buffer order a, w, sw, sa, out, bias, ..., lt, lb, lr).
+ *   C[m][n] = c_dtype(float(acc) * sa[m] * sw[n] + bias[n] + sum_{k0<=j<k1} T[m][j] * B[n][j]),
+ *   acc[m][n] = sum_k A[m][k] * W[n][k]  (exact, int32)
+ *   A     int8 [M][a_stride], K-contiguous        W   int8 [N][w_stride], K-contiguous
+ *   sw    fp32 [N]    sa  fp32 [M]    bias  fp32 [N] or NULL
+ *   C     [M][c_stride] of c_dtype: H3B_BF16 / H3B_F16 / H3B_F32, or H3B_I32 for the raw accumulators (scales,
+ *         bias and the low-rank term are then ignored)
+ *   lora_T  fp16 [M][t_stride] or NULL    lora_B  fp16 [N][b_stride]    R  ranks used (multiple of 32, <= 128)
+ *   lora_ranges  int32 [2 * ceil(N / h3b_gemm_tile_n(..))] = (k0, k1) per column tile, multiples of 16, or NULL for
+ *         the whole range 0..R (the reference's table `lr` without its two leading strides)
+ * All M rows are computed and stored (the caller passes its padded row count, as h3metal/ops.py:165 does).
+ * A, W, T, B must be 16-byte aligned with row strides that are multiples of 16 bytes. */
+H3B_API int h3b_gemm_w8a8(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
+                  const float *sw, const float *sa, const float *bias, void *C, int c_dtype, int64_t c_stride,
+                  int M, int N, int K, const void *lora_T, int64_t t_stride, const void *lora_B, int64_t b_stride,
+                  int R, const int32_t *lora_ranges);
+
+/* Column-tile width the product uses for N outputs with (lora != 0) or without a low-rank term: the granularity
+ * of lora_ranges. Plays the part of the TN macro the reference compiles into its kernel (kernels/gemm.metal:48-50). */
+H3B_API int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int lora);
+/* Overrides the product's choices: tile_n (0 = automatic; 32, 64, 128, 256) and band (row tiles swept per column
+ * tile, 0 = automatic). The counterpart of the tile= and swz= arguments of h3metal/ops.py:124-126. Returns 0. */
+H3B_API int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band);
+/* Threads-per-row target of the rotate+quantise kernel (0 = automatic). The counterpart of the NSG/MAXB geometry
+ * of h3metal/ops.py:193-197. Returns 0. */
+H3B_API int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target);
+
+/* Nothing is deferred on CUDA, so commit only exists for interface parity. Replaces h3_commit (src/capi.h:65). */
+H3B_API void h3b_commit(h3b_ctx *ctx);
+/* Blocks until the work launched through this context is done. Returns the GPU seconds between the first launch
+ * since the previous wait and the end of the last one, 0 if nothing was launched, or a negative value if a kernel
+ * failed or reported a device-side timeout (see h3b_last_error). Replaces h3_wait (src/capi.h:66-70). */
+H3B_API double h3b_wait(h3b_ctx *ctx);
+/* With profiling on every launch is timed on its own (and the host waits for it); h3b_profile_take returns the
+ * seconds recorded since the last call. Replace h3_set_profile / h3_profile_take (src/capi.h:71-74). */
+H3B_API void h3b_set_profile(h3b_ctx *ctx, int on);
+H3B_API int h3b_profile_take(h3b_ctx *ctx, double *seconds, int max);
+/* Kernels launched through this context since it was opened (the benchmark's launch count). No counterpart. */
+H3B_API uint64_t h3b_launch_count(h3b_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* H3B200_H */
