@@ -1,0 +1,371 @@
+"""Benchmark of the W8A8 Hadamard-linear path: the linears of one Z-Image-Turbo-shaped DiT block (M = 4608 tokens,
+hidden 3840: QKV 3840->11520, out 3840->3840, w1|w3 3840->20480, w2 10240->3840 fed by value*silu(gate)), each
+as rotate+quantise followed by the int8 product with bias. One "step" is one pass over the four linears
+(8 kernel launches) on synthetic, seeded data.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 1]
+
+With N > 1 (one process per GPU under torch.distributed.run) every rank runs the block on its own M tokens
+(token sharding: the path is row-independent, no collective is needed), and `value` is the total over ranks
+divided by the slowest rank's time. Rank 0 prints ONE JSON line.
+
+`--impl reference` times the reference's CPU (NumPy) arithmetic of the same path on the host cores, on a bounded
+row sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "dit_block_w8a8_linears_tokens_per_s"
+UNIT = "tokens/s"
+NOMINAL_INT8_TOPS = 4500.0  # B200 dense int8, datasheet
+
+
+def measured_peaks():
+    """HBM GB/s and int8 TOPS ceilings for the roofline: the pool's measured copy bandwidth and twice its measured
+    dense bf16 rate (int8 runs on the same tensor pipe at twice the bf16 rate), else the documented fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "int8_tops": 2.0 * float(p["bf16_tflops_sustained"]),
+                "source": "measured (MEASURED_PEAKS.json: hbm_gbs; 2 x bf16_tflops_sustained)"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "int8_tops": 2.0 * 1400.0, "source": "fallback (6.65 TB/s; 2 x 1.4 PFLOP/s sustained)"}
+
+
+# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu capture
+# summarised under profiles/), keyed by workload; None until a capture exists for it.
+NCU_TRAFFIC_BYTES = {}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+        self.t_from = self.t_to = None  # host-time window whose samples count (the GPU is under load in it)
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for stamp, r in self.rows:
+            if len(r) < 7 or (self.t_from is not None and not (self.t_from <= stamp <= self.t_to)):
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---- CPU arm: the reference's NumPy arithmetic of the path -------------------------------------------------------------
+class CpuBlock:
+    """Rotation as x.reshape(M, K/B, B) @ H in fp32, absmax int8 quantisation, product in float64 BLAS with the
+    scales and bias applied as the reference's tests write it (tests/test_gemm.py:31, tests/test_ops.py:15-18),
+    bf16 store. Weights are prepared (and widened to float64) once, outside the timed steps."""
+
+    def __init__(self, cfg, rows: int, seed: int = 0):
+        from oracle import quant_ref
+        self.q = quant_ref
+        self.cfg, self.rows = cfg, rows
+        rng = np.random.default_rng(seed)
+        self.layers = []
+        for spec in cfg.layers:
+            w = rng.integers(-127, 128, size=(spec.N, spec.K), dtype=np.int8)  # stands in for quantised weights
+            sw = rng.uniform(1e-4, 2e-4, size=spec.N).astype(np.float32)
+            bias = (rng.standard_normal(spec.N) * 0.01).astype(np.float32)
+            x = None
+            if not spec.swiglu_in:
+                x = quant_ref.bf16_round_bits(rng.standard_normal((rows, spec.K)).astype(np.float32))
+            self.layers.append((spec, np.ascontiguousarray(w.T.astype(np.float64)), sw, bias, x))
+
+    def step(self):
+        q = self.q
+        prev = None
+        for spec, wT, sw, bias, x in self.layers:
+            if spec.swiglu_in:
+                h = q.bf16_bits_to_f32(prev)
+                g = h[:, spec.K:]
+                xf = h[:, :spec.K] * (g / (1.0 + np.exp(-g)))
+            else:
+                xf = q.bf16_bits_to_f32(x)
+            r = q.rotate_in(xf, None, self.cfg.block)
+            amax = np.abs(r).max(axis=1)
+            s = np.where(amax > 0, amax / np.float32(127), np.float32(1)).astype(np.float32)
+            codes = np.rint(r * (np.float32(1) / s)[:, None])
+            y = (codes.astype(np.float64) @ wT) * s[:, None] * sw[None, :] + bias[None, :]
+            prev = q.bf16_round_bits(y.astype(np.float32))
+        return prev
+
+
+def time_cpu(cfg, rows: int, steps: int, warmup: int):
+    blk = CpuBlock(cfg, rows)
+    for _ in range(warmup):
+        blk.step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        blk.step()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return rows / dt, dt
+
+
+def host_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+        n = [p.get("num_threads", 0) for p in threadpool_info() if p.get("user_api") == "blas"]
+        if n:
+            return int(max(n))
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+# ---- arms ---------------------------------------------------------------------------------------------------------
+def run_reference(args, cfg, rank, world):
+    if rank != 0:
+        return None
+    rows = args.cpu_rows or 512
+    value, dt = time_cpu(cfg, rows, args.steps, args.warmup)
+    cores = host_threads()
+    sample = (f"{rows} of {cfg.M} rows of every linear of the block per step, NumPy fp32 rotation matmul + absmax int8 + "
+              f"float64 BLAS product + bias + bf16 store, weights widened once outside the timed steps")
+    return {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": workload_name(cfg), "block": cfg.block, "rows_per_step": rows},
+        "tops": value * cfg.ops / cfg.M / 1e12,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def workload_name(cfg) -> str:
+    from h3metal_b200 import workloads
+    number = next(k for k, v in workloads.CONFIGS.items() if v is cfg)
+    return f"config {number}: {cfg.name}, M={cfg.M}, " + ", ".join(f"{l.name} {l.K}->{l.N}" for l in cfg.layers)
+
+
+def run_ours(args, cfg, rank, world):
+    import torch
+    import torch.distributed as dist
+    from h3metal_b200.gpu import Gpu
+    from h3metal_b200.linear import BlockLinears
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    gpu = Gpu(device=local)
+    blk = BlockLinears(gpu, cfg, seed=1234 + rank)
+    dev = gpu.torch_device
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, steps):
+        """K calls of fn between two events on the launching stream; returns milliseconds (max over ranks)."""
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record(gpu.stream)
+        for _ in range(steps):
+            fn()
+        end.record(gpu.stream)
+        torch.cuda.synchronize(dev)
+        ms = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
+        barrier()
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- device-resident throughput: inputs already in HBM --------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        blk.step()
+    with ClockSampler(local) as clocks:
+        launches0 = gpu.launch_count
+        t_load = time.time()
+        ms = timed(blk.step, args.steps)
+        launches = gpu.launch_count - launches0
+        # The timed region lasts milliseconds, shorter than one nvidia-smi sample. Keep the same steps running back
+        # to back for about a second more so that the clock record is of this load; only samples taken from the
+        # start of the timed region to the end of this window count.
+        extra_steps = 0
+        while time.time() - t_load < 1.2:
+            for _ in range(args.steps):
+                blk.step()
+            extra_steps += args.steps
+            torch.cuda.synchronize(dev)
+        clocks.t_from, clocks.t_to = t_load, time.time()
+        time.sleep(0.15)  # let the sampler's last line arrive
+    gpu.wait()
+    tokens = cfg.M * world * args.steps
+    value = tokens / (ms * 1e-3)
+
+    # ---- per-kernel durations for the roofline: the same steps with an event pair around every launch ---------------
+    peaks = measured_peaks()
+    gemm_s = rot_s = 0.0
+    gemm_ops = rot_bytes = 0
+    gpu.profile(True)
+    for _ in range(args.steps):
+        blk.step()
+    for name, sec in gpu.profile_take():
+        if name.startswith("gemm"):
+            gemm_s += sec
+        else:
+            rot_s += sec
+    gpu.profile(False)
+    for l in blk.layers:
+        gemm_ops += 2 * l.m_pad * l.wt.K * l.wt.N * args.steps
+        rot_bytes += blk.M * ((4 if l.swiglu_in else 2) * l.wt.K + l.wt.K + 4) * args.steps
+    achieved_tops = gemm_ops / gemm_s / 1e12
+    rot_gbs = rot_bytes / rot_s / 1e9
+    wl = workload_name(cfg)
+    roofline = {"bound": "tensor", "kernel": "gemm_w8a8_kernel (tcgen05 kind::i8)", "achieved": achieved_tops,
+                "peak": peaks["int8_tops"], "unit": "TOP/s", "frac": achieved_tops / peaks["int8_tops"],
+                "traffic": NCU_TRAFFIC_BYTES.get(wl), "peak_source": peaks["source"],
+                "frac_of_nominal_4500": achieved_tops / NOMINAL_INT8_TOPS,
+                "time_share": gemm_s / (gemm_s + rot_s)}
+    roofline_rot = {"bound": "hbm", "kernel": "rot_q8_kernel", "achieved": rot_gbs, "peak": peaks["hbm_gbs"],
+                    "unit": "GB/s", "frac": rot_gbs / peaks["hbm_gbs"], "traffic": None,
+                    "time_share": rot_s / (gemm_s + rot_s)}
+
+    # ---- end to end through the public API with HOST buffers: H2D of every input, D2H of every output ---------------
+    host_in, host_out = [], []
+    for layer, x in zip(blk.layers, blk.inputs):
+        if x is not None:
+            host_in.append((torch.empty(x.shape, dtype=torch.bfloat16).pin_memory().copy_(x.torch().cpu()), x.torch()))
+    for i, layer in enumerate(blk.layers):
+        consumed = i + 1 < len(blk.layers) and blk.inputs[i + 1] is None  # feeds the next linear on the device
+        if not consumed:
+            host_out.append((torch.empty(layer.out.shape, dtype=torch.bfloat16).pin_memory(), layer.out.torch()))
+    h2d = sum(h.numel() * 2 for h, _ in host_in)
+    d2h = sum(h.numel() * 2 for h, _ in host_out)
+
+    def e2e_step():
+        with torch.cuda.stream(gpu.stream):
+            for h, d in host_in:
+                d.copy_(h, non_blocking=True)
+            blk.step()
+            for h, d in host_out:
+                h.copy_(d, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps)
+    e2e_value = tokens / (e2e_ms * 1e-3)
+
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        return None
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": wl, "block": cfg.block, "parallelism": f"token-sharded x{world} (no collective)",
+                   "l2": "per-step working set (int8 weights 177 MB + activations and outputs 0.5 GB) exceeds the 126 MB L2"},
+        "tops": value / cfg.M * cfg.ops / 1e12 ,
+        "roofline": roofline, "roofline_rot_q8": roofline_rot,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": int(launches),
+        "clocks": dict(clocks.summary(), window=f"timed region + {extra_steps} identical steps run straight after it"),
+    }
+    if world == 1 and not args.no_cpu:
+        rows = args.cpu_rows or 1024
+        cpu_value, cpu_dt = time_cpu(cfg, rows, 2, 1)
+        line["cpu_baseline"] = {
+            "value": cpu_value, "unit": UNIT, "cores": host_threads(), "kind": "port",
+            "sample": f"{rows} of {cfg.M} rows of every linear per step, 2 timed steps after 1 warm-up: the reference's NumPy "
+                      f"arithmetic (fp32 rotation matmul, absmax int8, float64 BLAS product, bias, bf16 store)"}
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=1)
+    ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (0 = default)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+
+    from h3metal_b200 import workloads
+    cfg = workloads.CONFIGS[args.config]
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+
+    if args.impl == "reference":
+        line = run_reference(args, cfg, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
+    try:
+        line = run_ours(args, cfg, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -210,7 +210,13 @@ int h3b_sm_count(h3b_ctx *ctx) { return ctx ? ctx->prop.multiProcessorCount : 0;
 
 int h3b_set_stream(h3b_ctx *ctx, void *cuda_stream) {
   if (!ctx) return fail("null context");
-  ctx->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
+  ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+  return 0;
+}
+
+int h3b_use_own_stream(h3b_ctx *ctx) {
+  if (!ctx) return fail("null context");
+  ctx->stream = ctx->own_stream;
   return 0;
 }
 
@@ -234,15 +240,16 @@ int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void 
   if (reinterpret_cast<uintptr_t>(x) % 16 || (x_stride * esize) % 16)
     return fail("rot_q8: input rows must be 16-byte aligned");
   if (reinterpret_cast<uintptr_t>(out) % 16) return fail("rot_q8: output must be 16-byte aligned");
-  int target = ctx->rot_threads > 0 ? ctx->rot_threads : 512;
+  int target = ctx->rot_threads > 0 ? ctx->rot_threads : 256;
   if (target < 32) target = 32;
-  if (target > 512) target = 512;
+  if (target > 256) target = 256;
   int ch, threads;
   h3b::rot_q8_geometry(D, target, &ch, &threads);
-  if (threads > 1024) return fail("rot_q8: D " + std::to_string(D) + " exceeds the 65536 channels one CTA covers");
+  if (threads > 256) return fail("rot_q8: D " + std::to_string(D) + " exceeds the 32768 channels one CTA covers");
   cudaEvent_t ps = nullptr;
   if (ctx->before_launch(&ps)) return -1;
-  const cudaError_t e = h3b::launch_rot_q8(x, x_dtype, x_stride, out, sa, M, D, block, mode, out_hr, target, ctx->stream);
+  const cudaError_t e = h3b::launch_rot_q8(x, x_dtype, x_stride, out, sa, M, D, block, mode, out_hr, target,
+                                           ctx->prop.multiProcessorCount, ctx->stream);
   return ctx->after_launch("rot_q8 launch", e);
 }
 

@@ -12,7 +12,7 @@ enum Dtype : int { kDtypeF32 = 0, kDtypeF16 = 1, kDtypeBf16 = 2, kDtypeI8 = 3, k
 
 void rot_q8_geometry(int D, int threads_target, int *ch, int *threads);
 cudaError_t launch_rot_q8(const void *x, int x_dtype, long long x_stride, void *out, float *sa, int M, int D,
-                          int block, int mode, int out_hr, int threads_target, cudaStream_t stream);
+                          int block, int mode, int out_hr, int threads_target, int sms, cudaStream_t stream);
 
 // Everything one launch of the int8 product needs. Tensor maps are built by the caller (capi.cu) because they
 // need the driver entry point and are cached per context.

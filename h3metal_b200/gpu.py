@@ -59,6 +59,7 @@ def _signatures():
         "h3b_max_buffer_length": (u64, [vp]),
         "h3b_sm_count": (i32, [vp]),
         "h3b_set_stream": (i32, [vp, vp]),
+        "h3b_use_own_stream": (i32, [vp]),
         "h3b_rot_q8": (i32, [vp, vp, i32, i64, vp, vp, i32, i32, i32, i32, i32]),
         "h3b_gemm_w8a8": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32, i32, vp, i64, vp, i64, i32,
                                 vp]),

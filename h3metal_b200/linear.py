@@ -1,0 +1,91 @@
+"""A quantised linear layer as the reference's transformer blocks run it: rotate + quantise the activations, then
+the int8 product with its epilogue (h3metal/dit.py:209-217, h3metal/zimage.py:328-345: `ops.rot_q8` followed by
+`ops.gemm`). `QuantLinear` owns the layer's device buffers so that a step launches kernels and nothing else;
+`BlockLinears` strings the linears of one transformer block together for the benchmark and the smoke test.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+from . import ops, workloads
+from .gpu import Gpu, Tensor
+
+
+class QuantLinear:
+    """y = W8A8(x): x bf16 [M][K] (or [M][2K] holding value | gate with swiglu_in) -> y [M][N] of out_dtype."""
+
+    def __init__(self, gpu: Gpu, wt: ops.QWeight, M: int, *, block: int = 128, swiglu_in: bool = False,
+                 out_dtype: str = "bf16"):
+        self.gpu, self.wt, self.M, self.block, self.swiglu_in = gpu, wt, M, block, swiglu_in
+        self.m_pad = ops.pad_rows(M)
+        self.a8 = gpu.empty((self.m_pad, wt.K), "i8")
+        self.sa = gpu.empty((self.m_pad,), "f32")
+        self.out = gpu.empty((self.m_pad, wt.N), out_dtype)
+
+    def __call__(self, x: Tensor, x_stride: int | None = None) -> Tensor:
+        ops.rot_q8(self.gpu, x, self.a8, self.sa, self.M, self.wt.K, swiglu=self.swiglu_in, x_stride=x_stride,
+                   block=self.block)
+        ops.gemm(self.gpu, self.a8, self.wt, self.out, self.M, sa=self.sa, tile=(128, 32, 4))
+        return self.out
+
+    @property
+    def launches_per_call(self) -> int:
+        return 3 if self.wt.low is not None else 2
+
+
+def upload_weight(gpu: Gpu, codes, scales, bias=None, low=None) -> ops.QWeight:
+    """QWeight from NumPy arrays or torch device tensors (int8 codes [N][K], fp32 scales [N], fp32 bias [N])."""
+    def put(t):
+        if t is None:
+            return None
+        return gpu.upload(t) if isinstance(t, np.ndarray) else gpu.wrap(t)
+    N, K = codes.shape
+    return ops.QWeight("q8", put(codes), put(scales), int(N), int(K), bias=put(bias), low=low)
+
+
+class BlockLinears:
+    """The linears of one transformer block of `cfg` on one GPU, with synthetic weights drawn on the device.
+
+    Layers whose input is the previous layer's output (swiglu_in) consume it; the others read their own input
+    buffer (in the model these come from the norm / attention kernels, which are not part of this path)."""
+
+    def __init__(self, gpu: Gpu, cfg: workloads.Config, seed: int = 0, M: int | None = None, layers=None):
+        import torch
+        self.gpu, self.cfg = gpu, cfg
+        self.M = M or cfg.M
+        gen = torch.Generator(device=gpu.torch_device)
+        gen.manual_seed(seed)
+        self.scratch = ops.Scratch(gpu)
+        self.layers, self.inputs = [], []
+        rng = np.random.default_rng(seed)
+        for spec in (layers or cfg.layers):
+            codes, scales = workloads.weight_torch(gen, spec.N, spec.K, gpu.torch_device)
+            bias = (torch.randn(spec.N, generator=gen, device=gpu.torch_device) * 0.01) if cfg.bias else None
+            low = None
+            if cfg.lora_rank:
+                A, B = workloads.lora_np(rng, cfg.lora_rank, spec.K, spec.N, cfg.block)
+                low = ops.low_rank(gpu, A, B, self.scratch)
+            wt = upload_weight(gpu, codes, scales, bias, low)
+            self.layers.append(QuantLinear(gpu, wt, self.M, block=cfg.block, swiglu_in=spec.swiglu_in))
+            if spec.swiglu_in:
+                self.inputs.append(None)
+            else:
+                x = workloads.activations_torch(gen, ops.pad_rows(self.M), spec.K, cfg.n_outliers(spec.K),
+                                                gpu.torch_device)
+                self.inputs.append(gpu.wrap(x))
+
+    def step(self):
+        """One pass over the block's linears: 2 launches per layer (3 with a LoRA term)."""
+        prev = None
+        for layer, x in zip(self.layers, self.inputs):
+            prev = layer(prev if x is None else x)
+        return prev
+
+    @property
+    def launches_per_step(self) -> int:
+        return sum(l.launches_per_call for l in self.layers)
+
+    @property
+    def ops_per_step(self) -> int:
+        return sum(2 * self.M * l.wt.K * l.wt.N for l in self.layers)

@@ -53,10 +53,13 @@ H3B_API uint64_t h3b_max_buffer_length(h3b_ctx *ctx);
 /* Number of SMs of the device (grid sizing of the persistent product kernel). No reference counterpart. */
 H3B_API int h3b_sm_count(h3b_ctx *ctx);
 
-/* Makes later launches go to `cuda_stream` (a cudaStream_t; NULL = the context's own stream), so that a host
- * that owns the tensors can order the kernels with its other work. No reference counterpart (Metal command
- * queues are owned by the reference's context, src/metal_rt.h:16-45). Returns 0. */
+/* Makes later launches go to `cuda_stream` (a cudaStream_t, taken as is: NULL is CUDA's legacy default stream,
+ * which is also PyTorch's default stream), so that a host that owns the tensors can order the kernels with its
+ * other work. h3b_use_own_stream returns to the non-blocking stream the context created at h3b_open, which is
+ * where launches go until h3b_set_stream is called. No reference counterpart (Metal command queues are owned by
+ * the reference's context, src/metal_rt.h:16-45). Both return 0. */
 H3B_API int h3b_set_stream(h3b_ctx *ctx, void *cuda_stream);
+H3B_API int h3b_use_own_stream(h3b_ctx *ctx);
 
 /* Rotate + per-token int8 quantise. Replaces the dispatch of the Metal kernel rot_q8
  * (kernels/ops.metal:274-334; parameter block RotQParams kernels/params.h:25-29; launcher h3metal/ops.py:214-222).

@@ -1,0 +1,148 @@
+"""rot_q8 on the GPU (through ops.rot_q8 -> ctypes -> h3b_rot_q8) against the CPU oracle.
+
+Acceptance: int8 codes bit-exact, at most 1 LSB on at most 1e-4 of the elements; scales within 2 ulp (bit-exact
+without the silu step, whose exp differs between math libraries in the last place)."""
+import numpy as np
+import pytest
+
+import oracle
+from h3metal_b200 import ops
+from tests.conftest import rel_fro
+
+pytestmark = pytest.mark.gpu
+
+ULP = 2.0 ** -23
+
+
+def _bits(rng, M, cols, scale=2.0, outliers=0, D=None):
+    x = (rng.standard_normal((M, cols)) * scale).astype(np.float32)
+    if outliers:
+        x[:, rng.choice(D or cols, size=outliers, replace=False)] *= 20.0
+    return x
+
+
+def _run(gpu, xh, dtype, M, D, block, swiglu, x_stride=None, out_hr=False):
+    X = gpu.upload(xh, dtype)
+    out = gpu.empty((M, D), "f16" if out_hr else "i8")
+    sa = gpu.empty((M,), "f32")
+    ops.rot_q8(gpu, X, out, None if out_hr else sa, M, D, swiglu=swiglu, block=block, x_stride=x_stride, out_hr=out_hr)
+    gpu.wait()
+    return out.numpy(), sa.numpy()
+
+
+def _check_codes(gq, gs, q, s, exact):
+    diff = np.abs(gq.astype(np.int32) - q.astype(np.int32))
+    if exact:
+        assert diff.max() == 0, f"{int((diff != 0).sum())} codes differ"
+        assert np.array_equal(gs, s)
+    else:
+        assert diff.max() <= 1 and (diff != 0).mean() <= 1e-4
+        assert np.all(np.abs(gs - s) <= 2 * ULP * np.abs(s))
+
+
+@pytest.mark.parametrize("block", [64, 128, 256])
+@pytest.mark.parametrize("M,D", [(1, 256), (19, 512), (7, 3072), (33, 3840), (5, 6144), (9, 16384), (3, 32768),
+                                 (127, 768), (129, 1280)])
+def test_plain_bf16_bit_exact(gpu, block, M, D):
+    if D % block:
+        pytest.skip("D not a multiple of the block")
+    rng = np.random.default_rng(M * 131 + D + block)
+    xh = oracle.bf16_round_bits(_bits(rng, M, D, outliers=min(8, D // 64)))
+    gq, gs = _run(gpu, xh, "bf16", M, D, block, False)
+    q, s = oracle.rot_q8_rows(xh, D, block=block, dtype="bf16")
+    _check_codes(gq, gs, q, s, exact=True)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+@pytest.mark.parametrize("block", [64, 128, 256])
+def test_other_input_types_bit_exact(gpu, dtype, block):
+    rng = np.random.default_rng(7 + block)
+    x = _bits(rng, 21, 2048)
+    xh = x.astype(np.float16) if dtype == "f16" else x
+    gq, gs = _run(gpu, xh, dtype, 21, 2048, block, False)
+    q, s = oracle.rot_q8_rows(xh, 2048, block=block, dtype=dtype)
+    _check_codes(gq, gs, q, s, exact=True)
+
+
+@pytest.mark.parametrize("block,M,D", [(256, 19, 14336), (128, 33, 10240), (128, 17, 16384), (64, 8, 1024)])
+def test_swiglu_within_budget(gpu, block, M, D):
+    """value * silu(gate): same shapes as the reference's tests/test_ops.py:55 (D=14336) plus the configs' FFN widths."""
+    rng = np.random.default_rng(2)
+    xh = oracle.bf16_round_bits(_bits(rng, M, 2 * D))
+    gq, gs = _run(gpu, xh, "bf16", M, D, block, True)
+    q, s = oracle.rot_q8_rows(xh, D, block=block, dtype="bf16", swiglu=True)
+    _check_codes(gq, gs, q, s, exact=False)
+    # the reference's own bound (tests/test_ops.py:69-72): dequantised codes within 0.6/127 of the float64 rotation
+    xf = oracle.bf16_bits_to_f32(xh).astype(np.float64)
+    g = xf[:, D:]
+    want = oracle.rotate_rows_matmul((xf[:, :D] * g / (1 + np.exp(-g))).astype(np.float32), block)
+    got = gq.astype(np.float64) * gs[:, None]
+    assert np.abs(got - want).max() / np.abs(want).max() < 0.6 / 127
+
+
+def test_reference_golden_rotation_bound(gpu, golden):
+    """Expected rotations computed by the reference's tests/test_ops.py rot() (stored in tests/golden)."""
+    xh = golden["rot_x_bits"]
+    for swiglu, key in ((False, "rot_expect_plain_f64"), (True, "rot_expect_swiglu_f64")):
+        want = golden[key]
+        gq, gs = _run(gpu, xh, "bf16", 5, 768, 256, swiglu, x_stride=1536)
+        assert np.abs(gq.astype(np.float64) * gs[:, None] - want).max() / np.abs(want).max() < 0.6 / 127
+        half, _ = _run(gpu, xh, "bf16", 5, 768, 256, swiglu, x_stride=1536, out_hr=True)
+        assert np.abs(half.astype(np.float64) - want).max() / np.abs(want).max() < 2e-3
+
+
+@pytest.mark.parametrize("block", [128, 256])
+def test_rotated_half_output(gpu, block):
+    rng = np.random.default_rng(11)
+    xh = oracle.bf16_round_bits(_bits(rng, 13, 1536))
+    half, _ = _run(gpu, xh, "bf16", 13, 1536, block, False, out_hr=True)
+    assert np.array_equal(half, oracle.rot_q8_rows(xh, 1536, block=block, out_hr=True))
+
+
+def test_zero_rows_and_strided_view(gpu):
+    """An all-zero row gets scale 1 and zero codes (kernels/ops.metal:316); a row stride wider than the row reads a
+    view of a larger buffer (h3metal/flux2.py:477 passes one)."""
+    rng = np.random.default_rng(3)
+    x = _bits(rng, 6, 1024)
+    x[2] = 0
+    xh = oracle.bf16_round_bits(x)
+    gq, gs = _run(gpu, xh, "bf16", 6, 512, 128, False, x_stride=1024)
+    q, s = oracle.rot_q8_rows(xh[:, :512], 512, block=128)
+    _check_codes(gq, gs, q, s, exact=True)
+    assert gs[2] == 1.0 and not gq[2].any()
+
+
+def test_every_row_uses_the_full_code_range(gpu):
+    """Size-independent property at a configuration's full size (M=17408 rows of 6144 channels): each non-zero row
+    has a code of magnitude 127, scale * 127 equals the largest rotated magnitude, and dequantised codes reproduce
+    the rotation within half a step (checked on a sample of rows against the oracle, bit for bit)."""
+    import torch
+    M, D, block = 17408, 6144, 128
+    gen = torch.Generator(device=gpu.torch_device)
+    gen.manual_seed(5)
+    x = torch.randn(M, D, generator=gen, device=gpu.torch_device).to(torch.bfloat16)
+    out, sa = gpu.empty((M, D), "i8"), gpu.empty((M,), "f32")
+    ops.rot_q8(gpu, gpu.wrap(x), out, sa, M, D, block=block)
+    gpu.wait()
+    codes = out.torch()
+    assert int(codes.to(torch.int16).abs().amax(dim=1).min()) == 127
+    rows = np.unique(np.r_[0:16, M - 16:M, np.random.default_rng(0).integers(0, M, 64)])
+    xh = x[torch.as_tensor(rows, device=x.device)].view(torch.int16).cpu().numpy().view(np.uint16)
+    q, s = oracle.rot_q8_rows(xh, D, block=block)
+    assert np.array_equal(codes[torch.as_tensor(rows, device=x.device)].cpu().numpy(), q)
+    assert np.array_equal(sa.torch()[torch.as_tensor(rows, device=x.device)].cpu().numpy(), s)
+
+
+def test_bad_arguments_are_refused(gpu):
+    from h3metal_b200.gpu import GpuError
+    x = gpu.empty((4, 512), "bf16")
+    out, sa = gpu.empty((4, 512), "i8"), gpu.empty((4,), "f32")
+    with pytest.raises(ValueError):
+        ops.rot_q8(gpu, x, out, sa, 4, 500, block=128)
+    with pytest.raises(GpuError):
+        ops.rot_q8(gpu, x, out, sa, 4, 512, block=32)
+    with pytest.raises(GpuError):
+        ops.rot_q8(gpu, x, out, sa, 4, 512, block=128, x_stride=500)
+    with pytest.raises(GpuError):
+        ops.rot_q8(gpu, x.view((4, 256), offset_elems=1), out, sa, 4, 256, block=128, x_stride=512)  # misaligned
+    gpu.wait()
