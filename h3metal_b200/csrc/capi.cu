@@ -33,20 +33,21 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_
 
 struct MapKey {
   const void *ptr;
-  uint64_t inner, rows, stride_bytes;
-  uint32_t box_inner, box_rows;
-  int dtype, swizzle;
+  uint64_t dims[3], strides[2];  // extents (innermost first) and byte strides of dimensions 1 and 2
+  uint32_t box[3];
+  int rank, dtype, swizzle;
   bool operator==(const MapKey &o) const {
-    return ptr == o.ptr && inner == o.inner && rows == o.rows && stride_bytes == o.stride_bytes &&
-           box_inner == o.box_inner && box_rows == o.box_rows && dtype == o.dtype && swizzle == o.swizzle;
+    return ptr == o.ptr && rank == o.rank && dtype == o.dtype && swizzle == o.swizzle &&
+           memcmp(dims, o.dims, sizeof dims) == 0 && memcmp(strides, o.strides, sizeof strides) == 0 &&
+           memcmp(box, o.box, sizeof box) == 0;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey &k) const {
     uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
-    for (uint64_t v : {k.inner, k.rows, k.stride_bytes, static_cast<uint64_t>(k.box_inner),
-                       static_cast<uint64_t>(k.box_rows), static_cast<uint64_t>(k.dtype),
-                       static_cast<uint64_t>(k.swizzle)})
+    for (uint64_t v : {k.dims[0], k.dims[1], k.dims[2], k.strides[0], k.strides[1], static_cast<uint64_t>(k.box[0]),
+                       static_cast<uint64_t>(k.box[1]), static_cast<uint64_t>(k.box[2]), static_cast<uint64_t>(k.rank),
+                       static_cast<uint64_t>(k.dtype), static_cast<uint64_t>(k.swizzle)})
       h = (h ^ v) * 0x100000001B3ull;
     return static_cast<size_t>(h);
   }
@@ -58,6 +59,7 @@ const char *status_text(int code) {
     case 2: return "MMA issuer timed out waiting for operands or a free accumulator";
     case 3: return "epilogue timed out waiting for an accumulator";
     case 4: return "wind-down timed out waiting for copies in flight";
+    case 5: return "rotate+quantise kernel timed out waiting for a row to arrive in shared memory";
     default: return "unknown device status";
   }
 }
@@ -77,7 +79,7 @@ struct h3b_ctx {
   int *status_host = nullptr;  // pinned copy read at wait
   EncodeTiledFn encode = nullptr;
   std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
-  int tile_n_override = 0, band_override = 0, rot_threads = 0;
+  int tile_n_override = 0, band_override = 0, rot_threads = 0, rot_stages = 0;
   uint64_t launches = 0;
   std::string name;
 
@@ -111,25 +113,47 @@ struct h3b_ctx {
     }
     return 0;
   }
+  // 2-D map of a row-major [rows][inner] tensor with a box of box_rows x box_inner elements.
   const CUtensorMap *tensor_map(const void *ptr, int dtype, uint64_t inner, uint64_t rows, uint64_t stride_bytes,
                                 uint32_t box_inner, uint32_t box_rows, int swizzle) {
-    const MapKey key{ptr, inner, rows, stride_bytes, box_inner, box_rows, dtype, swizzle};
+    MapKey key{};
+    key.ptr = ptr; key.rank = 2; key.dtype = dtype; key.swizzle = swizzle;
+    key.dims[0] = inner; key.dims[1] = rows; key.dims[2] = 1;
+    key.strides[0] = stride_bytes; key.strides[1] = 0;
+    key.box[0] = box_inner; key.box[1] = box_rows; key.box[2] = 1;
+    return build_map(key);
+  }
+  // 3-D map {d0, d1, d2} (d0 innermost) with byte strides s1, s2 and a box {b0, b1, 1}.
+  const CUtensorMap *tensor_map3(const void *ptr, int dtype, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1,
+                                 uint64_t s2, uint32_t b0, uint32_t b1, int swizzle) {
+    MapKey key{};
+    key.ptr = ptr; key.rank = 3; key.dtype = dtype; key.swizzle = swizzle;
+    key.dims[0] = d0; key.dims[1] = d1; key.dims[2] = d2;
+    key.strides[0] = s1; key.strides[1] = s2;
+    key.box[0] = b0; key.box[1] = b1; key.box[2] = 1;
+    return build_map(key);
+  }
+  const CUtensorMap *build_map(const MapKey &key) {
     auto it = maps.find(key);
     if (it != maps.end()) return &it->second;
     CUtensorMap m;
-    const cuuint64_t dims[2] = {inner, rows};
-    const cuuint64_t strides[1] = {stride_bytes};
-    const cuuint32_t box[2] = {box_inner, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapDataType dt = dtype == h3b::kDtypeF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-    const CUtensorMapSwizzle sw = swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-    const CUresult r = encode(&m, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const cuuint64_t dims[3] = {key.dims[0], key.dims[1], key.dims[2]};
+    const cuuint64_t strides[2] = {key.strides[0], key.strides[1]};
+    const cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapDataType dt = key.dtype == h3b::kDtypeI8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : key.dtype == h3b::kDtypeBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapSwizzle sw = key.swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    const CUresult r = encode(&m, dt, static_cast<cuuint32_t>(key.rank), const_cast<void *>(key.ptr), dims, strides, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-      char buf[256];
+      char buf[320];
       snprintf(buf, sizeof buf,
-               "cuTensorMapEncodeTiled failed (%d) for ptr %p inner %llu rows %llu stride %llu box %u x %u", (int)r, ptr,
-               (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)stride_bytes, box_inner, box_rows);
+               "cuTensorMapEncodeTiled failed (%d) for ptr %p rank %d dims %llu x %llu x %llu strides %llu, %llu box %u x %u",
+               (int)r, key.ptr, key.rank, (unsigned long long)dims[0], (unsigned long long)dims[1],
+               (unsigned long long)dims[2], (unsigned long long)strides[0], (unsigned long long)strides[1], box[0], box[1]);
       fail(buf);
       return nullptr;
     }
@@ -220,9 +244,11 @@ int h3b_use_own_stream(h3b_ctx *ctx) {
   return 0;
 }
 
-int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target) {
+int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target, int tma_stages) {
   if (!ctx) return fail("null context");
+  if (tma_stages < -1 || tma_stages > 4) return fail("rot policy: tma_stages must be -1 (off), 0 (automatic) or 1..4");
   ctx->rot_threads = threads_target;
+  ctx->rot_stages = tma_stages;
   return 0;
 }
 
@@ -240,13 +266,24 @@ int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void 
   if (reinterpret_cast<uintptr_t>(x) % 16 || (x_stride * esize) % 16)
     return fail("rot_q8: input rows must be 16-byte aligned");
   if (reinterpret_cast<uintptr_t>(out) % 16) return fail("rot_q8: output must be 16-byte aligned");
+  cudaEvent_t ps = nullptr;
+  if (ctx->rot_stages >= 0 && h3b::rot_q8_tma_supported(x_dtype, D)) {
+    // rows reach shared memory by TMA: the input seen as {64 channels, cols / 64 chunks, M rows}
+    const uint64_t cols = mode == 1 ? 2ull * D : static_cast<uint64_t>(D);
+    const CUtensorMap *map = ctx->tensor_map3(x, x_dtype, 64, cols / 64, M, 128, static_cast<uint64_t>(x_stride) * 2, 64,
+                                              static_cast<uint32_t>(D / 64), 128);
+    if (!map) return -1;
+    if (ctx->before_launch(&ps)) return -1;
+    const cudaError_t e = h3b::launch_rot_q8_tma(*map, x_dtype, out, sa, M, D, block, mode, out_hr, ctx->rot_stages,
+                                                 ctx->prop.multiProcessorCount, ctx->status_dev, ctx->stream);
+    return ctx->after_launch("rot_q8 launch", e);
+  }
   int target = ctx->rot_threads > 0 ? ctx->rot_threads : 256;
   if (target < 32) target = 32;
   if (target > 256) target = 256;
   int ch, threads;
   h3b::rot_q8_geometry(D, target, &ch, &threads);
   if (threads > 256) return fail("rot_q8: D " + std::to_string(D) + " exceeds the 32768 channels one CTA covers");
-  cudaEvent_t ps = nullptr;
   if (ctx->before_launch(&ps)) return -1;
   const cudaError_t e = h3b::launch_rot_q8(x, x_dtype, x_stride, out, sa, M, D, block, mode, out_hr, target,
                                            ctx->prop.multiProcessorCount, ctx->stream);

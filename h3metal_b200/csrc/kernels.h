@@ -14,6 +14,14 @@ void rot_q8_geometry(int D, int threads_target, int *ch, int *threads);
 cudaError_t launch_rot_q8(const void *x, int x_dtype, long long x_stride, void *out, float *sa, int M, int D,
                           int block, int mode, int out_hr, int threads_target, int sms, cudaStream_t stream);
 
+// TMA-fed variant for bf16 / fp16 inputs of up to 16384 channels. `map` describes the input as
+// {64, cols / 64, M} with box {64, D / 64, 1} and 128-byte swizzle (built by the caller).
+bool rot_q8_tma_supported(int x_dtype, int D);
+void rot_q8_tma_plan(int D, int mode, int stages_wanted, int *threads, int *stages, int *stage_bytes, int *gate_offset,
+                     size_t *smem);
+cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, float *sa, int M, int D, int block,
+                              int mode, int out_hr, int stages_wanted, int sms, int *status, cudaStream_t stream);
+
 // Everything one launch of the int8 product needs. Tensor maps are built by the caller (capi.cu) because they
 // need the driver entry point and are cached per context.
 struct GemmLaunch {

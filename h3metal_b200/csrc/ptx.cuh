@@ -16,6 +16,7 @@ enum DeviceStatus : int {
   kStatusMmaTimeout = 2,        // MMA issuer waited too long for operands or for a free accumulator
   kStatusEpilogueTimeout = 3,   // epilogue waited too long for an accumulator
   kStatusDrainTimeout = 4,      // wind-down waited too long for copies in flight
+  kStatusRotTimeout = 5,        // rotate+quantise kernel waited too long for a row to arrive in shared memory
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -88,6 +89,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// 3-D tile load (x innermost). Same completion mechanism as the 2-D form.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 

@@ -14,14 +14,16 @@
 //
 // Mapping to the GPU. The kernel is bound by HBM traffic only if it also stays under the SM's instruction issue
 // rate (at full bandwidth an SM has about 16 issue slots per channel), so the layout minimises instructions:
-//   * a thread owns `CH` chunks of 32 consecutive channels (four 128-bit loads per bf16/fp16 chunk, two 128-bit
-//     stores of int8 codes); the five butterfly stages of stride 1..16 run in its registers, the last four of them
+//   * a thread owns `CH` chunks of 64 consecutive channels (eight 128-bit loads per bf16/fp16 chunk, four 128-bit
+//     stores of int8 codes); the six butterfly stages of stride 1..32 run in its registers, the last five of them
 //     as packed two-wide fp32 operations (add.f32x2 / fma.f32x2, each lane rounded like the scalar operation);
-//   * only the stages of stride 32 and up cross lanes: one shuffle stage for a block of 64, two for 128, three
-//     for 256, inside groups of 2, 4 or 8 neighbouring lanes, written as o + sign * v (exact product, one rounding);
+//   * only the stages of stride 64 and up cross lanes (shuffles are the scarcest resource here): none for a block
+//     of 64, one for 128, two for 256, between 2 or 4 neighbouring lanes, written as o + sign * v (the product is
+//     exact, so the fma rounds once, like the add or subtract it stands for);
 //   * CTAs are persistent: a CTA walks rows m = blockIdx.x, += gridDim.x and issues the loads of its next row
-//     before it transforms the current one, so every thread always has CH x 64 bytes in flight;
-//   * the row maximum goes through a warp shuffle reduction and one shared-memory exchange per row.
+//     before it transforms the current one, so every thread always has CH x 128 bytes in flight;
+//   * a CTA is as many warps as the row needs (one warp covers 2048 channels per chunk); the row maximum is a
+//     warp shuffle reduction plus, only when the row spans several warps, one shared-memory exchange per row.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -32,11 +34,12 @@
 #include <mutex>
 
 #include "kernels.h"
+#include "rot_common.cuh"
 
 namespace h3b {
 namespace {
 
-constexpr int kChunk = 32;  // consecutive channels a thread owns per chunk
+using namespace rot;
 
 struct RotQArgs {
   const void *x;
@@ -47,118 +50,9 @@ struct RotQArgs {
   float normaliser;    // fp32(1 / sqrt(block))
 };
 
-__device__ __forceinline__ uint4 ld_stream16(const void *p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
-// Raw (still packed) input of one chunk: 64 bytes for 16-bit inputs, 128 bytes for fp32.
-template <typename IN_T>
-struct RawChunk {
-  static constexpr int kVec = kChunk * sizeof(IN_T) / 16;
-  uint4 q[kVec];
-  __device__ __forceinline__ void load(const IN_T *p) {
-#pragma unroll
-    for (int i = 0; i < kVec; ++i) q[i] = ld_stream16(reinterpret_cast<const uint4 *>(p) + i);
-  }
-  __device__ __forceinline__ void zero() {
-#pragma unroll
-    for (int i = 0; i < kVec; ++i) q[i] = make_uint4(0u, 0u, 0u, 0u);
-  }
-};
-
-__device__ __forceinline__ void widen(const RawChunk<__nv_bfloat16> &r, float (&v)[kChunk]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t w[4] = {r.q[i].x, r.q[i].y, r.q[i].z, r.q[i].w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
-      v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
-    }
-  }
-}
-__device__ __forceinline__ void widen(const RawChunk<__half> &r, float (&v)[kChunk]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t w[4] = {r.q[i].x, r.q[i].y, r.q[i].z, r.q[i].w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
-      v[8 * i + 2 * j] = f.x;
-      v[8 * i + 2 * j + 1] = f.y;
-    }
-  }
-}
-__device__ __forceinline__ void widen(const RawChunk<float> &r, float (&v)[kChunk]) {
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    v[4 * i] = __uint_as_float(r.q[i].x);
-    v[4 * i + 1] = __uint_as_float(r.q[i].y);
-    v[4 * i + 2] = __uint_as_float(r.q[i].z);
-    v[4 * i + 3] = __uint_as_float(r.q[i].w);
-  }
-}
-
-// x / (1 + exp(-x)): accurate expf, then one correctly rounded division.
-__device__ __forceinline__ float silu(float g) { return __fdiv_rn(g, __fadd_rn(1.0f, expf(-g))); }
-
-// In-thread butterfly stages of stride 1, 2, 4, 8, 16 over the chunk's 32 values. Stride 1 pairs the two halves of
-// a float2 and stays scalar; the others combine whole float2 registers: a + b and fma(b, -1, a) = a - b.
-__device__ __forceinline__ void chunk_butterflies(float (&v)[kChunk]) {
-#pragma unroll
-  for (int i = 0; i < kChunk; i += 2) {
-    const float a = v[i], b = v[i + 1];
-    v[i] = __fadd_rn(a, b);
-    v[i + 1] = __fsub_rn(a, b);
-  }
-  const float2 minus_one = make_float2(-1.0f, -1.0f);
-#pragma unroll
-  for (int s = 2; s < kChunk; s <<= 1) {
-#pragma unroll
-    for (int i = 0; i < kChunk; i += 2) {
-      if ((i & s) == 0) {
-        const float2 a = make_float2(v[i], v[i + 1]), b = make_float2(v[i + s], v[i + s + 1]);
-        const float2 sum = __fadd2_rn(a, b), dif = __ffma2_rn(b, minus_one, a);
-        v[i] = sum.x; v[i + 1] = sum.y;
-        v[i + s] = dif.x; v[i + s + 1] = dif.y;
-      }
-    }
-  }
-}
-
-// Stages of stride 32 .. BLOCK/2: the partner value lives in lane ^ (stride / 32). The lower lane keeps v + o, the
-// upper lane o - v; both are o + sign * v with sign = +-1 (the product is exact, so the fma rounds once).
-template <int BLOCK>
-__device__ __forceinline__ void lane_butterflies(float (&v)[kChunk], int lane) {
-#pragma unroll
-  for (int s = 1; s < BLOCK / kChunk; s <<= 1) {
-    const float sg = (lane & s) ? -1.0f : 1.0f;
-    const float2 sign = make_float2(sg, sg);
-#pragma unroll
-    for (int i = 0; i < kChunk; i += 2) {
-      const float2 o = make_float2(__shfl_xor_sync(0xFFFFFFFFu, v[i], s), __shfl_xor_sync(0xFFFFFFFFu, v[i + 1], s));
-      const float2 r = __ffma2_rn(make_float2(v[i], v[i + 1]), sign, o);
-      v[i] = r.x; v[i + 1] = r.y;
-    }
-  }
-}
-
-__device__ __forceinline__ uint32_t pack4_s8(int a, int b, int c, int d) {
-  // two saturating s32 -> s8 packs: {c, d} into the low half of a temporary, then {a, b} below it... the
-  // instruction puts its first source in byte 1 and its second in byte 0 and shifts the third operand up.
-  uint32_t hi, r;
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
-  return r;
-}
-
 template <typename IN_T, int BLOCK, int CH, bool SWIGLU, bool OUT_HR>
 __global__ void __launch_bounds__(256) rot_q8_kernel(const RotQArgs p) {
-  __shared__ float warp_max[2][32];
+  __shared__ float warp_max[2][8];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n_warps = blockDim.x >> 5;
   const int n_chunks = p.D / kChunk;
@@ -217,7 +111,7 @@ __global__ void __launch_bounds__(256) rot_q8_kernel(const RotQArgs p) {
         const int chunk = tid + c * blockDim.x;
         if (chunk < n_chunks) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < kChunk / 8; ++q) {
             uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -232,12 +126,14 @@ __global__ void __launch_bounds__(256) rot_q8_kernel(const RotQArgs p) {
       // row maximum: lanes, then warps (buffers alternate between rows so one barrier per row is enough)
 #pragma unroll
       for (int s = 16; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, s));
-      float *wm = warp_max[it & 1];
-      if (lane == 0) wm[warp] = amax;
-      __syncthreads();
-      float row_max = lane < n_warps ? wm[lane] : 0.0f;
-#pragma unroll
-      for (int s = 16; s > 0; s >>= 1) row_max = fmaxf(row_max, __shfl_xor_sync(0xFFFFFFFFu, row_max, s));
+      float row_max = amax;
+      if (n_warps > 1) {
+        float *wm = warp_max[it & 1];
+        if (lane == 0) wm[warp] = amax;
+        __syncthreads();
+        row_max = wm[0];
+        for (int w = 1; w < n_warps; ++w) row_max = fmaxf(row_max, wm[w]);
+      }
 
       const float scale = row_max > 0.0f ? __fdiv_rn(row_max, 127.0f) : 1.0f;
       const float rs = __fdiv_rn(1.0f, scale);
@@ -247,17 +143,17 @@ __global__ void __launch_bounds__(256) rot_q8_kernel(const RotQArgs p) {
       for (int c = 0; c < CH; ++c) {
         const int chunk = tid + c * blockDim.x;
         if (chunk < n_chunks) {
-          uint32_t w[8];
+          uint32_t w[kChunk / 4];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < kChunk / 4; ++j) {
             const float2 y0 = __fmul2_rn(make_float2(v[c][4 * j], v[c][4 * j + 1]), rs2);
             const float2 y1 = __fmul2_rn(make_float2(v[c][4 * j + 2], v[c][4 * j + 3]), rs2);
             // round to nearest, ties to even; |y| <= 127 up to rounding, so the saturating pack never clips
             w[j] = pack4_s8(__float2int_rn(y0.x), __float2int_rn(y0.y), __float2int_rn(y1.x), __float2int_rn(y1.y));
           }
           uint4 *d4 = reinterpret_cast<uint4 *>(dst + chunk * kChunk);
-          d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+#pragma unroll
+          for (int j = 0; j < kChunk / 16; ++j) d4[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
         }
       }
       if (tid == 0) p.sa[m] = scale;
@@ -302,8 +198,7 @@ template <typename IN_T, int BLOCK>
 cudaError_t launch_ch(const RotQArgs &a, int ch, int threads, int sms, int mode, int out_hr, cudaStream_t stream) {
   switch (ch) {
     case 1: return launch_mode<IN_T, BLOCK, 1>(a, threads, sms, mode, out_hr, stream);
-    case 2: return launch_mode<IN_T, BLOCK, 2>(a, threads, sms, mode, out_hr, stream);
-    default: return launch_mode<IN_T, BLOCK, 4>(a, threads, sms, mode, out_hr, stream);
+    default: return launch_mode<IN_T, BLOCK, 2>(a, threads, sms, mode, out_hr, stream);
   }
 }
 
@@ -319,12 +214,12 @@ cudaError_t launch_block(const RotQArgs &a, int block, int ch, int threads, int 
 
 }  // namespace
 
-// Chunks per thread (1, 2 or 4) and CTA size for a row of D channels: the fewest chunks per thread that keep the
-// CTA at or under `threads_target` threads (CTAs are limited to 256 threads by register use).
+// Chunks per thread (1 or 2) and CTA size for a row of D channels: the fewest chunks per thread that keep the
+// CTA at or under `threads_target` threads (CTAs are limited to 256 threads, 8 warps, by the row-maximum exchange).
 void rot_q8_geometry(int D, int threads_target, int *ch, int *threads) {
-  const int n_chunks = D / kChunk;
+  const int n_chunks = (D + kChunk - 1) / kChunk;
   int c = 1;
-  while (c < 4 && (n_chunks + c - 1) / c > threads_target) c <<= 1;
+  while (c < 2 && (n_chunks + c - 1) / c > threads_target) c <<= 1;
   int t = (n_chunks + c - 1) / c;
   t = (t + 31) / 32 * 32;
   *ch = c;

@@ -65,7 +65,7 @@ def _signatures():
                                 vp]),
         "h3b_gemm_tile_n": (i32, [vp, i32, i32]),
         "h3b_gemm_set_policy": (i32, [vp, i32, i32]),
-        "h3b_rot_set_policy": (i32, [vp, i32]),
+        "h3b_rot_set_policy": (i32, [vp, i32, i32]),
         "h3b_commit": (None, [vp]),
         "h3b_wait": (dbl, [vp]),
         "h3b_set_profile": (None, [vp, i32]),
@@ -291,10 +291,11 @@ class Gpu:
     def gemm_tile_n(self, N: int, lora: bool) -> int:
         return lib().h3b_gemm_tile_n(self.ctx, N, int(lora))
 
-    def set_policy(self, tile_n: int = 0, band: int = 0, rot_threads: int = 0):
-        """Overrides of the library's own choices (0 = automatic), for tuning sweeps."""
+    def set_policy(self, tile_n: int = 0, band: int = 0, rot_threads: int = 0, rot_stages: int = 0):
+        """Overrides of the library's own choices (0 = automatic), for tuning sweeps and for tests that want a
+        particular kernel variant. rot_stages = -1 selects the register-fed rotate+quantise kernel."""
         self._check(lib().h3b_gemm_set_policy(self.ctx, tile_n, band))
-        self._check(lib().h3b_rot_set_policy(self.ctx, rot_threads))
+        self._check(lib().h3b_rot_set_policy(self.ctx, rot_threads, rot_stages))
 
     # -- execution ------------------------------------------------------------------------------------------------
     def launch(self, k: Kernel, grid, threads, args, params: bytes = b"", params_index: int | None = None,

@@ -97,9 +97,11 @@ H3B_API int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int lora);
 /* Overrides the product's choices: tile_n (0 = automatic; 32, 64, 128, 256) and band (row tiles swept per column
  * tile, 0 = automatic). The counterpart of the tile= and swz= arguments of h3metal/ops.py:124-126. Returns 0. */
 H3B_API int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band);
-/* Threads-per-row target of the rotate+quantise kernel (0 = automatic). The counterpart of the NSG/MAXB geometry
- * of h3metal/ops.py:193-197. Returns 0. */
-H3B_API int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target);
+/* Tuning of the rotate+quantise kernel. tma_stages: rows a CTA keeps in flight in shared memory (1..4), 0 =
+ * automatic, -1 = do not use the TMA-fed kernel. threads_target: CTA size target of the register-fed kernel that
+ * serves fp32 inputs, rows over 16384 channels and tma_stages = -1 (0 = automatic). The counterpart of the NSG/MAXB
+ * geometry of h3metal/ops.py:193-197. Returns 0. */
+H3B_API int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target, int tma_stages);
 
 /* Nothing is deferred on CUDA, so commit only exists for interface parity. Replaces h3_commit (src/capi.h:65). */
 H3B_API void h3b_commit(h3b_ctx *ctx);

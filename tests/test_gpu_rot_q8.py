@@ -1,7 +1,8 @@
 """rot_q8 on the GPU (through ops.rot_q8 -> ctypes -> h3b_rot_q8) against the CPU oracle.
 
-Acceptance: int8 codes bit-exact, at most 1 LSB on at most 1e-4 of the elements; scales within 2 ulp (bit-exact
-without the silu step, whose exp differs between math libraries in the last place)."""
+Acceptance: int8 codes bit-exact, at most 1 LSB on at most 1e-4 of the elements; scales bit-exact without the
+silu step and within 4 units in the last place with it (exp and the division inside silu differ between math
+libraries in their last places, and the row maximum inherits that)."""
 import numpy as np
 import pytest
 
@@ -11,7 +12,12 @@ from tests.conftest import rel_fro
 
 pytestmark = pytest.mark.gpu
 
-ULP = 2.0 ** -23
+
+
+def ulp_distance(a, b):
+    """Distance between positive fp32 values in units in the last place (difference of their bit patterns)."""
+    return np.abs(a.astype(np.float32).view(np.int32).astype(np.int64) - b.astype(np.float32).view(np.int32).astype(np.int64))
+
 
 
 def _bits(rng, M, cols, scale=2.0, outliers=0, D=None):
@@ -21,12 +27,19 @@ def _bits(rng, M, cols, scale=2.0, outliers=0, D=None):
     return x
 
 
-def _run(gpu, xh, dtype, M, D, block, swiglu, x_stride=None, out_hr=False):
+def _run(gpu, xh, dtype, M, D, block, swiglu, x_stride=None, out_hr=False, variant="tma"):
+    """variant: "tma" = the library's choice (rows staged in shared memory by TMA for 16-bit inputs of up to 16384
+    channels), "tma2" / "tma4" = the same with a ring of 2 / 4 rows, "regs" = the register-fed kernel."""
     X = gpu.upload(xh, dtype)
     out = gpu.empty((M, D), "f16" if out_hr else "i8")
     sa = gpu.empty((M,), "f32")
-    ops.rot_q8(gpu, X, out, None if out_hr else sa, M, D, swiglu=swiglu, block=block, x_stride=x_stride, out_hr=out_hr)
-    gpu.wait()
+    gpu.set_policy(rot_stages={"tma": 0, "tma2": 2, "tma4": 4, "regs": -1}[variant])
+    try:
+        ops.rot_q8(gpu, X, out, None if out_hr else sa, M, D, swiglu=swiglu, block=block, x_stride=x_stride,
+                   out_hr=out_hr)
+        gpu.wait()
+    finally:
+        gpu.set_policy()
     return out.numpy(), sa.numpy()
 
 
@@ -37,18 +50,19 @@ def _check_codes(gq, gs, q, s, exact):
         assert np.array_equal(gs, s)
     else:
         assert diff.max() <= 1 and (diff != 0).mean() <= 1e-4
-        assert np.all(np.abs(gs - s) <= 2 * ULP * np.abs(s))
+        assert ulp_distance(gs, s).max() <= 4
 
 
+@pytest.mark.parametrize("variant", ["tma", "regs"])
 @pytest.mark.parametrize("block", [64, 128, 256])
 @pytest.mark.parametrize("M,D", [(1, 256), (19, 512), (7, 3072), (33, 3840), (5, 6144), (9, 16384), (3, 32768),
-                                 (127, 768), (129, 1280)])
-def test_plain_bf16_bit_exact(gpu, block, M, D):
+                                 (127, 768), (129, 1280), (1500, 2048)])
+def test_plain_bf16_bit_exact(gpu, variant, block, M, D):
     if D % block:
         pytest.skip("D not a multiple of the block")
     rng = np.random.default_rng(M * 131 + D + block)
     xh = oracle.bf16_round_bits(_bits(rng, M, D, outliers=min(8, D // 64)))
-    gq, gs = _run(gpu, xh, "bf16", M, D, block, False)
+    gq, gs = _run(gpu, xh, "bf16", M, D, block, False, variant=variant)
     q, s = oracle.rot_q8_rows(xh, D, block=block, dtype="bf16")
     _check_codes(gq, gs, q, s, exact=True)
 
@@ -60,16 +74,20 @@ def test_other_input_types_bit_exact(gpu, dtype, block):
     x = _bits(rng, 21, 2048)
     xh = x.astype(np.float16) if dtype == "f16" else x
     gq, gs = _run(gpu, xh, dtype, 21, 2048, block, False)
+    rq, rs = _run(gpu, xh, dtype, 21, 2048, block, False, variant="regs")
+    assert np.array_equal(gq, rq) and np.array_equal(gs, rs)
     q, s = oracle.rot_q8_rows(xh, 2048, block=block, dtype=dtype)
     _check_codes(gq, gs, q, s, exact=True)
 
 
-@pytest.mark.parametrize("block,M,D", [(256, 19, 14336), (128, 33, 10240), (128, 17, 16384), (64, 8, 1024)])
-def test_swiglu_within_budget(gpu, block, M, D):
+@pytest.mark.parametrize("variant", ["tma", "tma2", "tma4", "regs"])
+@pytest.mark.parametrize("block,M,D", [(256, 19, 14336), (128, 33, 10240), (128, 17, 16384), (64, 8, 1024),
+                                       (128, 700, 1280)])
+def test_swiglu_within_budget(gpu, variant, block, M, D):
     """value * silu(gate): same shapes as the reference's tests/test_ops.py:55 (D=14336) plus the configs' FFN widths."""
     rng = np.random.default_rng(2)
     xh = oracle.bf16_round_bits(_bits(rng, M, 2 * D))
-    gq, gs = _run(gpu, xh, "bf16", M, D, block, True)
+    gq, gs = _run(gpu, xh, "bf16", M, D, block, True, variant=variant)
     q, s = oracle.rot_q8_rows(xh, D, block=block, dtype="bf16", swiglu=True)
     _check_codes(gq, gs, q, s, exact=False)
     # the reference's own bound (tests/test_ops.py:69-72): dequantised codes within 0.6/127 of the float64 rotation
@@ -91,22 +109,24 @@ def test_reference_golden_rotation_bound(gpu, golden):
         assert np.abs(half.astype(np.float64) - want).max() / np.abs(want).max() < 2e-3
 
 
+@pytest.mark.parametrize("variant", ["tma", "regs"])
 @pytest.mark.parametrize("block", [128, 256])
-def test_rotated_half_output(gpu, block):
+def test_rotated_half_output(gpu, variant, block):
     rng = np.random.default_rng(11)
     xh = oracle.bf16_round_bits(_bits(rng, 13, 1536))
-    half, _ = _run(gpu, xh, "bf16", 13, 1536, block, False, out_hr=True)
+    half, _ = _run(gpu, xh, "bf16", 13, 1536, block, False, out_hr=True, variant=variant)
     assert np.array_equal(half, oracle.rot_q8_rows(xh, 1536, block=block, out_hr=True))
 
 
-def test_zero_rows_and_strided_view(gpu):
+@pytest.mark.parametrize("variant", ["tma", "tma4", "regs"])
+def test_zero_rows_and_strided_view(gpu, variant):
     """An all-zero row gets scale 1 and zero codes (kernels/ops.metal:316); a row stride wider than the row reads a
     view of a larger buffer (h3metal/flux2.py:477 passes one)."""
     rng = np.random.default_rng(3)
     x = _bits(rng, 6, 1024)
     x[2] = 0
     xh = oracle.bf16_round_bits(x)
-    gq, gs = _run(gpu, xh, "bf16", 6, 512, 128, False, x_stride=1024)
+    gq, gs = _run(gpu, xh, "bf16", 6, 512, 128, False, x_stride=1024, variant=variant)
     q, s = oracle.rot_q8_rows(xh[:, :512], 512, block=128)
     _check_codes(gq, gs, q, s, exact=True)
     assert gs[2] == 1.0 and not gq[2].any()
