@@ -9,6 +9,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -137,6 +138,12 @@ struct h3b_ctx {
     auto it = maps.find(key);
     if (it != maps.end()) return &it->second;
     CUtensorMap m;
+    if (encode_map(key, &m)) return nullptr;
+    if (maps.size() > 4096) maps.clear();  // bound the cache; descriptors are cheap to rebuild
+    return &maps.emplace(key, m).first->second;
+  }
+  // Encodes a descriptor into caller-provided storage (touches no cache, allocates nothing). 0 on success.
+  int encode_map(const MapKey &key, CUtensorMap *out) {
     const cuuint64_t dims[3] = {key.dims[0], key.dims[1], key.dims[2]};
     const cuuint64_t strides[2] = {key.strides[0], key.strides[1]};
     const cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
@@ -145,7 +152,7 @@ struct h3b_ctx {
                                  : key.dtype == h3b::kDtypeBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUtensorMapSwizzle sw = key.swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-    const CUresult r = encode(&m, dt, static_cast<cuuint32_t>(key.rank), const_cast<void *>(key.ptr), dims, strides, box,
+    const CUresult r = encode(out, dt, static_cast<cuuint32_t>(key.rank), const_cast<void *>(key.ptr), dims, strides, box,
                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -154,11 +161,20 @@ struct h3b_ctx {
                "cuTensorMapEncodeTiled failed (%d) for ptr %p rank %d dims %llu x %llu x %llu strides %llu, %llu box %u x %u",
                (int)r, key.ptr, key.rank, (unsigned long long)dims[0], (unsigned long long)dims[1],
                (unsigned long long)dims[2], (unsigned long long)strides[0], (unsigned long long)strides[1], box[0], box[1]);
-      fail(buf);
-      return nullptr;
+      return fail(buf);
     }
-    if (maps.size() > 4096) maps.clear();  // bound the cache; descriptors are cheap to rebuild
-    return &maps.emplace(key, m).first->second;
+    return 0;
+  }
+  // 2-D descriptor either from the cache or, with cached == false, encoded into *local.
+  const CUtensorMap *map2(bool cached, CUtensorMap *local, const void *ptr, int dtype, uint64_t inner, uint64_t rows,
+                          uint64_t stride_bytes, uint32_t box_inner, uint32_t box_rows, int swizzle) {
+    if (cached) return tensor_map(ptr, dtype, inner, rows, stride_bytes, box_inner, box_rows, swizzle);
+    MapKey key{};
+    key.ptr = ptr; key.rank = 2; key.dtype = dtype; key.swizzle = swizzle;
+    key.dims[0] = inner; key.dims[1] = rows; key.dims[2] = 1;
+    key.strides[0] = stride_bytes; key.strides[1] = 0;
+    key.box[0] = box_inner; key.box[1] = box_rows; key.box[2] = 1;
+    return encode_map(key, local) ? nullptr : local;
   }
 };
 
@@ -309,10 +325,12 @@ int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int /*lora*/) {
   return 128;
 }
 
-int h3b_gemm_w8a8(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
-                  const float *sw, const float *sa, const float *bias, void *C, int c_dtype, int64_t c_stride,
-                  int M, int N, int K, const void *lora_T, int64_t t_stride, const void *lora_B, int64_t b_stride,
-                  int R, const int32_t *lora_ranges) {
+// Checks the arguments of one product and enqueues it. cached_maps: TMA descriptors come from (and go into) the
+// context's cache; false builds them on the stack so that the call allocates nothing, host memory included.
+static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
+                        const float *sw, const float *sa, const float *bias, void *C, int c_dtype, int64_t c_stride,
+                        int M, int N, int K, const void *lora_T, int64_t t_stride, const void *lora_B,
+                        int64_t b_stride, int R, const int32_t *lora_ranges, bool cached_maps) {
   if (!ctx) return fail("null context");
   if (!A || !W || !C) return fail("gemm: null tensor argument");
   if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: M, N and K must be positive");
@@ -340,14 +358,15 @@ int h3b_gemm_w8a8(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t 
   h3b::GemmLaunch g;
   memset(&g, 0, sizeof g);
   const CUtensorMap *m;
-  if (!(m = ctx->tensor_map(A, h3b::kDtypeI8, K, M, a_stride, 128, 128, 128))) return -1;
+  CUtensorMap local;
+  if (!(m = ctx->map2(cached_maps, &local, A, h3b::kDtypeI8, K, M, a_stride, 128, 128, 128))) return -1;
   g.map_a = *m;
-  if (!(m = ctx->tensor_map(W, h3b::kDtypeI8, K, N, w_stride, 128, bn, 128))) return -1;
+  if (!(m = ctx->map2(cached_maps, &local, W, h3b::kDtypeI8, K, N, w_stride, 128, bn, 128))) return -1;
   g.map_w = *m;
   if (lora) {
-    if (!(m = ctx->tensor_map(lora_T, h3b::kDtypeF16, R, M, t_stride * 2, 32, 128, 64))) return -1;
+    if (!(m = ctx->map2(cached_maps, &local, lora_T, h3b::kDtypeF16, R, M, t_stride * 2, 32, 128, 64))) return -1;
     g.map_t = *m;
-    if (!(m = ctx->tensor_map(lora_B, h3b::kDtypeF16, R, N, b_stride * 2, 32, bn, 64))) return -1;
+    if (!(m = ctx->map2(cached_maps, &local, lora_B, h3b::kDtypeF16, R, N, b_stride * 2, 32, bn, 64))) return -1;
     g.map_b = *m;
   }
   g.sw = sw; g.sa = sa; g.bias = raw ? nullptr : bias; g.c = C; g.ranges = lora ? lora_ranges : nullptr;
@@ -371,6 +390,72 @@ int h3b_gemm_w8a8(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t 
   if (ctx->before_launch(&ps)) return -1;
   const cudaError_t e = h3b::launch_gemm_w8a8(g, stages, ctx->stream);
   return ctx->after_launch("gemm launch", e);
+}
+
+int h3b_gemm_w8a8(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
+                  const float *sw, const float *sa, const float *bias, void *C, int c_dtype, int64_t c_stride,
+                  int M, int N, int K, const void *lora_T, int64_t t_stride, const void *lora_B, int64_t b_stride,
+                  int R, const int32_t *lora_ranges) {
+  return gemm_enqueue(ctx, A, a_stride, W, w_stride, sw, sa, bias, C, c_dtype, c_stride, M, N, K, lora_T, t_stride,
+                      lora_B, b_stride, R, lora_ranges, true);
+}
+
+// ---- the product with a LoRA term for callers that cannot allocate ------------------------------------------------
+// Its T scratch lives in the library image instead of in caller memory: a file-scope device array. In host code the
+// array's NAME is only a stand-in for the symbol, not a device address, so the address is fetched once per device
+// with cudaGetSymbolAddress (below) and that pointer is what the kernels and the TMA descriptor receive.
+static __device__ __align__(256) unsigned short g_lora_t_static[H3B_NOALLOC_MAX_T_VALUES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void *g_static_addr[kMaxDevices] = {};
+
+// Device address of g_lora_t_static on the context's device (which the caller has made current). Looked up on the
+// first call per device and remembered.
+void *static_scratch(h3b_ctx *ctx) {
+  if (ctx->device < 0 || ctx->device >= kMaxDevices) {
+    fail("no-alloc product: device index out of range");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_addr[ctx->device]) {
+    void *ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_lora_t_static);
+    if (e != cudaSuccess || !ptr) {
+      fail_cuda("cudaGetSymbolAddress(static LoRA scratch)", e == cudaSuccess ? cudaErrorUnknown : e);
+      return nullptr;
+    }
+    g_static_addr[ctx->device] = ptr;
+  }
+  return g_static_addr[ctx->device];
+}
+}  // namespace
+
+int h3b_gemm_w8a8_lora_noalloc(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
+                               const float *sw, const float *sa, const float *bias, void *C, int c_dtype,
+                               int64_t c_stride, int M, int N, int K, const int8_t *lora_A, int64_t la_stride,
+                               const float *lora_sw, const void *lora_B, int64_t b_stride, int R,
+                               const int32_t *lora_ranges) {
+  if (!ctx) return fail("null context");
+  if (!lora_A || !lora_sw || !lora_B) return fail("no-alloc product: the low-rank term needs A codes, A scales and B");
+  if (c_dtype == H3B_I32) return fail("no-alloc product: raw accumulators carry no low-rank term; use h3b_gemm_w8a8");
+  if (M <= 0 || R <= 0 || R % 32 || R > 128) return fail("no-alloc product: R must be a multiple of 32, at most 128");
+  const unsigned long long need = static_cast<unsigned long long>(M) * static_cast<unsigned long long>(R);
+  if (need > H3B_NOALLOC_MAX_T_VALUES)
+    return fail("no-alloc product: M x R = " + std::to_string(need) + " fp16 values exceed the library's static scratch of " +
+                std::to_string(static_cast<unsigned long long>(H3B_NOALLOC_MAX_T_VALUES)) +
+                " (8 MiB); split the rows or use h3b_gemm_w8a8 with your own T buffer");
+  if (ctx->make_current()) return -1;
+  void *T = static_scratch(ctx);
+  if (!T) return -1;
+  // T[m][j] = fp16(acc * sa[m] * lora_sw[j]) for every one of the M rows and R columns: the whole region the main
+  // product reads is overwritten, so nothing of an earlier call survives into this one and nothing needs clearing.
+  if (gemm_enqueue(ctx, A, a_stride, lora_A, la_stride, lora_sw, sa, nullptr, T, H3B_F16, R, M, R, K, nullptr, 0, nullptr,
+                   0, 0, nullptr, false))
+    return -1;
+  return gemm_enqueue(ctx, A, a_stride, W, w_stride, sw, sa, bias, C, c_dtype, c_stride, M, N, K, T, R, lora_B, b_stride,
+                      R, lora_ranges, false);
 }
 
 void h3b_commit(h3b_ctx *) {}

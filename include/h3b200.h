@@ -91,6 +91,34 @@ H3B_API int h3b_gemm_w8a8(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const
                   int M, int N, int K, const void *lora_T, int64_t t_stride, const void *lora_B, int64_t b_stride,
                   int R, const int32_t *lora_ranges);
 
+/* The product with a LoRA term for callers that cannot allocate device memory. It has no counterpart in the
+ * reference (whose Scratch object, h3metal/ops.py:37-47, simply grows a buffer on demand).
+ *
+ * Who needs it: a host that was handed a fixed set of buffers and owns none of the device's memory itself. Two
+ * examples are an inference server whose allocator reserved the whole of HBM at start-up, so that a cudaMalloc
+ * from a plug-in fails or fights that allocator, and a serving loop with a latency bound, where cudaMalloc /
+ * cudaFree would synchronise the whole device in the middle of a step. h3b_gemm_w8a8 asks such a caller for a T
+ * buffer of M x R fp16 values; this entry point brings its own: T lives in a static device array inside the library
+ * image, H3B_NOALLOC_MAX_T_VALUES fp16 values (8 MiB), which every GPU that loads the library holds until the
+ * process exits. The call performs no cudaMalloc, cudaFree or other allocating call, and its TMA descriptors are
+ * built on the stack.
+ *
+ * It computes T = fp16((A x lora_A^T) * sa[m] * lora_sw[j]) into that array and then the same product as
+ * h3b_gemm_w8a8 with lora_T pointing at it; arguments as there, except that the term's input side is passed as its
+ * int8 codes lora_A [R][la_stride] and fp32 scales lora_sw [R] (what ops.low_rank() stores) instead of a finished T.
+ * Returns non-zero with a message if M x R exceeds H3B_NOALLOC_MAX_T_VALUES.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ * outside any stream capture. All calls on a device share the one array and each overwrites the part it uses in
+ * full: calls that overlap on the GPU (two streams, two contexts on the same device) race on it - keep them on one
+ * stream or order them yourself. */
+#define H3B_NOALLOC_MAX_T_VALUES (4u << 20)
+H3B_API int h3b_gemm_w8a8_lora_noalloc(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W,
+                                       int64_t w_stride, const float *sw, const float *sa, const float *bias, void *C,
+                                       int c_dtype, int64_t c_stride, int M, int N, int K, const int8_t *lora_A,
+                                       int64_t la_stride, const float *lora_sw, const void *lora_B, int64_t b_stride,
+                                       int R, const int32_t *lora_ranges);
+
 /* Column-tile width the product uses for N outputs with (lora != 0) or without a low-rank term: the granularity
  * of lora_ranges. Plays the part of the TN macro the reference compiles into its kernel (kernels/gemm.metal:48-50). */
 H3B_API int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int lora);
