@@ -204,8 +204,10 @@ def run_ours(args, cfg, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     gpu = Gpu(device=local)
-    blk = BlockLinears(gpu, cfg, seed=1234 + rank)
     dev = gpu.torch_device
+    if args.parallel == "tp":
+        return run_tensor_parallel(args, cfg, rank, world, gpu)
+    blk = BlockLinears(gpu, cfg, seed=1234 + rank)
 
     def barrier():
         if world > 1:
@@ -330,6 +332,43 @@ def run_ours(args, cfg, rank, world):
     return line
 
 
+def run_tensor_parallel(args, cfg, rank, world, gpu):
+    """One block of cfg.M tokens over all ranks: QKV and w1|w3 column-parallel, out and w2 row-parallel with a MAX
+    all-reduce of the row maxima and a SUM all-reduce of the partial products. Strong scaling; device-resident."""
+    import torch
+    import torch.distributed as dist
+    from h3metal_b200.parallel import TensorParallelBlock
+    if world == 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29531")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=gpu.torch_device)
+    blk = TensorParallelBlock(gpu, None, cfg, seed=99, reduce=args.reduce)
+    dev = gpu.torch_device
+    for _ in range(max(args.warmup, 3)):
+        blk.step()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize(dev)
+    start.record(gpu.stream)
+    for _ in range(args.steps):
+        blk.step()
+    end.record(gpu.stream)
+    torch.cuda.synchronize(dev)
+    ms = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    gpu.wait()
+    if rank != 0:
+        return None
+    ms = float(ms.item())
+    value = cfg.M * args.steps / (ms * 1e-3)
+    return {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": workload_name(cfg), "block": cfg.block,
+                       "parallelism": f"tp{world}: column-parallel qkv/w1w3, row-parallel out/w2 ({args.reduce} all-reduce)"},
+            "tops": value / cfg.M * cfg.ops / 1e12, "gpu_launches": None}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -339,6 +378,11 @@ def main():
     ap.add_argument("--config", type=int, default=1)
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (0 = default)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--parallel", default="token", choices=["token", "tp"],
+                    help="N > 1: token = every rank its own M tokens (default, weak scaling); tp = ONE block of M tokens "
+                         "sharded column-/row-parallel over the ranks with NCCL all-reduces (strong scaling)")
+    ap.add_argument("--reduce", default="int32", choices=["int32", "f32", "bf16"],
+                    help="tp: what the row-parallel layers all-reduce (int32 = bit-exact)")
     args = ap.parse_args()
 
     from h3metal_b200 import workloads

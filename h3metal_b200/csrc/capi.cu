@@ -268,10 +268,11 @@ int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target, int tma_stages) {
   return 0;
 }
 
-int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, float *sa, int M, int D,
-               int block, int mode, int out_hr) {
+static int rot_enqueue(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, float *sa, int M, int D,
+                       int block, int mode, int out_hr, int scale_mode) {
   if (!ctx) return fail("null context");
-  if (!x || !out || (!out_hr && !sa)) return fail("rot_q8: null tensor argument");
+  if (!x || (!out && scale_mode != 1) || (!out_hr && !sa)) return fail("rot_q8: null tensor argument");
+  if (scale_mode < 0 || scale_mode > 2 || (scale_mode && out_hr)) return fail("rot_q8: bad scale mode");
   if (M <= 0 || D <= 0) return fail("rot_q8: M and D must be positive");
   if (block != 64 && block != 128 && block != 256) return fail("rot_q8: rotation block must be 64, 128 or 256");
   if (D % block) return fail("rot_q8: D " + std::to_string(D) + " is not a multiple of the rotation block " + std::to_string(block));
@@ -281,7 +282,7 @@ int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void 
   if (x_stride < (mode == 1 ? 2LL * D : D)) return fail("rot_q8: x_stride is smaller than the row");
   if (reinterpret_cast<uintptr_t>(x) % 16 || (x_stride * esize) % 16)
     return fail("rot_q8: input rows must be 16-byte aligned");
-  if (reinterpret_cast<uintptr_t>(out) % 16) return fail("rot_q8: output must be 16-byte aligned");
+  if (out && reinterpret_cast<uintptr_t>(out) % 16) return fail("rot_q8: output must be 16-byte aligned");
   cudaEvent_t ps = nullptr;
   if (ctx->rot_stages >= 0 && h3b::rot_q8_tma_supported(x_dtype, D)) {
     // rows reach shared memory by TMA: the input seen as {64 channels, cols / 64 chunks, M rows}
@@ -290,7 +291,7 @@ int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void 
                                               static_cast<uint32_t>(D / 64), 128);
     if (!map) return -1;
     if (ctx->before_launch(&ps)) return -1;
-    const cudaError_t e = h3b::launch_rot_q8_tma(*map, x_dtype, out, sa, M, D, block, mode, out_hr, ctx->rot_stages,
+    const cudaError_t e = h3b::launch_rot_q8_tma(*map, x_dtype, out, sa, M, D, block, mode, out_hr, scale_mode, ctx->rot_stages,
                                                  ctx->prop.multiProcessorCount, ctx->status_dev, ctx->stream);
     return ctx->after_launch("rot_q8 launch", e);
   }
@@ -301,9 +302,37 @@ int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void 
   h3b::rot_q8_geometry(D, target, &ch, &threads);
   if (threads > 256) return fail("rot_q8: D " + std::to_string(D) + " exceeds the 32768 channels one CTA covers");
   if (ctx->before_launch(&ps)) return -1;
-  const cudaError_t e = h3b::launch_rot_q8(x, x_dtype, x_stride, out, sa, M, D, block, mode, out_hr, target,
+  const cudaError_t e = h3b::launch_rot_q8(x, x_dtype, x_stride, out, sa, M, D, block, mode, out_hr, scale_mode, target,
                                            ctx->prop.multiProcessorCount, ctx->stream);
   return ctx->after_launch("rot_q8 launch", e);
+}
+
+int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, float *sa, int M, int D,
+               int block, int mode, int out_hr) {
+  return rot_enqueue(ctx, x, x_dtype, x_stride, out, sa, M, D, block, mode, out_hr, 0);
+}
+
+int h3b_rot_amax(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, float *amax, int M, int D, int block,
+                 int mode) {
+  return rot_enqueue(ctx, x, x_dtype, x_stride, nullptr, amax, M, D, block, mode, 0, 1);
+}
+
+int h3b_rot_q8_given_amax(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, float *amax_to_scale,
+                          int M, int D, int block, int mode) {
+  return rot_enqueue(ctx, x, x_dtype, x_stride, out, amax_to_scale, M, D, block, mode, 0, 2);
+}
+
+int h3b_dequant_i32(h3b_ctx *ctx, const int32_t *acc, int64_t acc_stride, const float *sa, const float *sw,
+                    const float *bias, void *C, int c_dtype, int64_t c_stride, int M, int N) {
+  if (!ctx) return fail("null context");
+  if (!acc || !sa || !sw || !C) return fail("dequant: null tensor argument");
+  if (M <= 0 || N <= 0 || acc_stride < N || c_stride < N) return fail("dequant: bad sizes");
+  if (c_dtype != H3B_BF16 && c_dtype != H3B_F16 && c_dtype != H3B_F32) return fail("dequant: output type must be bf16, f16 or f32");
+  cudaEvent_t ps = nullptr;
+  if (ctx->before_launch(&ps)) return -1;
+  const cudaError_t e = h3b::launch_dequant_i32(acc, acc_stride, sa, sw, bias, C, c_dtype, c_stride, M, N,
+                                                ctx->prop.multiProcessorCount, ctx->stream);
+  return ctx->after_launch("dequant launch", e);
 }
 
 int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band) {

@@ -12,7 +12,8 @@ enum Dtype : int { kDtypeF32 = 0, kDtypeF16 = 1, kDtypeBf16 = 2, kDtypeI8 = 3, k
 
 void rot_q8_geometry(int D, int threads_target, int *ch, int *threads);
 cudaError_t launch_rot_q8(const void *x, int x_dtype, long long x_stride, void *out, float *sa, int M, int D,
-                          int block, int mode, int out_hr, int threads_target, int sms, cudaStream_t stream);
+                          int block, int mode, int out_hr, int scale_mode, int threads_target, int sms,
+                          cudaStream_t stream);
 
 // TMA-fed variant for bf16 / fp16 inputs of up to 16384 channels. `map` describes the input as
 // {64, cols / 64, M} with box {64, D / 64, 1} and 128-byte swizzle (built by the caller).
@@ -20,7 +21,14 @@ bool rot_q8_tma_supported(int x_dtype, int D);
 void rot_q8_tma_plan(int D, int mode, int stages_wanted, int *threads, int *stages, int *stage_bytes, int *gate_offset,
                      size_t *smem);
 cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, float *sa, int M, int D, int block,
-                              int mode, int out_hr, int stages_wanted, int sms, int *status, cudaStream_t stream);
+                              int mode, int out_hr, int scale_mode, int stages_wanted, int sms, int *status,
+                              cudaStream_t stream);
+
+// out[m][n] = c_dtype(float(acc[m][n]) * sa[m] * sw[n] + bias[n]): the product's epilogue applied to accumulators
+// that were summed elsewhere (row-parallel layers reduce their int32 partial accumulators over the GPUs first).
+cudaError_t launch_dequant_i32(const int32_t *acc, long long acc_stride, const float *sa, const float *sw,
+                               const float *bias, void *out, int c_dtype, long long c_stride, int M, int N, int sms,
+                               cudaStream_t stream);
 
 // Everything one launch of the int8 product needs. Tensor maps are built by the caller (capi.cu) because they
 // need the driver entry point and are cached per context.

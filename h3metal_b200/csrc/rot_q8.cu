@@ -48,6 +48,7 @@ struct RotQArgs {
   long long x_stride;  // elements between input rows
   int M, D;
   float normaliser;    // fp32(1 / sqrt(block))
+  int scale_mode;      // 0: scale from this row's maximum; 1: only write the maximum to sa; 2: sa holds the maximum to use
 };
 
 template <typename IN_T, int BLOCK, int CH, bool SWIGLU, bool OUT_HR>
@@ -135,6 +136,11 @@ __global__ void __launch_bounds__(256) rot_q8_kernel(const RotQArgs p) {
         for (int w = 1; w < n_warps; ++w) row_max = fmaxf(row_max, wm[w]);
       }
 
+      if (p.scale_mode == 1) {  // a shard of a longer row: hand the local maximum to the caller
+        if (tid == 0) p.sa[m] = row_max;
+        continue;
+      }
+      if (p.scale_mode == 2) row_max = p.sa[m];  // the whole row's maximum, reduced over the shards
       const float scale = row_max > 0.0f ? __fdiv_rn(row_max, 127.0f) : 1.0f;
       const float rs = __fdiv_rn(1.0f, scale);
       const float2 rs2 = make_float2(rs, rs);
@@ -227,9 +233,10 @@ void rot_q8_geometry(int D, int threads_target, int *ch, int *threads) {
 }
 
 cudaError_t launch_rot_q8(const void *x, int x_dtype, long long x_stride, void *out, float *sa, int M, int D,
-                          int block, int mode, int out_hr, int threads_target, int sms, cudaStream_t stream) {
+                          int block, int mode, int out_hr, int scale_mode, int threads_target, int sms,
+                          cudaStream_t stream) {
   RotQArgs a;
-  a.x = x; a.out = out; a.sa = sa; a.x_stride = x_stride; a.M = M; a.D = D;
+  a.x = x; a.out = out; a.sa = sa; a.x_stride = x_stride; a.M = M; a.D = D; a.scale_mode = scale_mode;
   a.normaliser = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
   int ch, threads;
   rot_q8_geometry(D, threads_target, &ch, &threads);

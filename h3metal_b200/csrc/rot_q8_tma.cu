@@ -40,6 +40,7 @@ struct RotTmaArgs {
   int stage_bytes;     // bytes per stage (value row, then gate row; each padded to 1024)
   int gate_offset;     // offset of the gate row inside a stage
   float normaliser;
+  int scale_mode;      // 0: scale from this row's maximum; 1: only write the maximum to sa; 2: sa holds the maximum to use
 };
 
 // 64 consecutive 16-bit values of chunk `t` of a stage, widened to fp32.
@@ -145,6 +146,11 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
     }
     float row_max = wm[0];
     for (int w = 1; w < n_warps; ++w) row_max = fmaxf(row_max, wm[w]);
+    if (!OUT_HR && p.scale_mode == 1) {  // a shard of a longer row: hand the local maximum to the caller
+      if (tid == 0) p.sa[m] = row_max;
+      continue;
+    }
+    if (!OUT_HR && p.scale_mode == 2) row_max = p.sa[m];  // the whole row's maximum, reduced over the shards
 
     if constexpr (OUT_HR) {
       if (active) {
@@ -255,9 +261,10 @@ void rot_q8_tma_plan(int D, int mode, int stages_wanted, int *threads, int *stag
 }
 
 cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, float *sa, int M, int D, int block,
-                              int mode, int out_hr, int stages_wanted, int sms, int *status, cudaStream_t stream) {
+                              int mode, int out_hr, int scale_mode, int stages_wanted, int sms, int *status,
+                              cudaStream_t stream) {
   RotTmaArgs a;
-  a.map = map; a.out = out; a.sa = sa; a.status = status; a.M = M; a.D = D;
+  a.map = map; a.out = out; a.sa = sa; a.status = status; a.M = M; a.D = D; a.scale_mode = scale_mode;
   a.normaliser = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
   int threads;
   size_t smem;

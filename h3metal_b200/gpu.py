@@ -61,6 +61,9 @@ def _signatures():
         "h3b_set_stream": (i32, [vp, vp]),
         "h3b_use_own_stream": (i32, [vp]),
         "h3b_rot_q8": (i32, [vp, vp, i32, i64, vp, vp, i32, i32, i32, i32, i32]),
+        "h3b_rot_amax": (i32, [vp, vp, i32, i64, vp, i32, i32, i32, i32]),
+        "h3b_rot_q8_given_amax": (i32, [vp, vp, i32, i64, vp, vp, i32, i32, i32, i32]),
+        "h3b_dequant_i32": (i32, [vp, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32]),
         "h3b_gemm_w8a8": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32, i32, vp, i64, vp, i64, i32,
                                 vp]),
         "h3b_gemm_w8a8_lora_noalloc": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32, i32, vp, i64, vp,
@@ -278,6 +281,26 @@ class Gpu:
                                       sa.ptr if sa is not None else None, M, D, block, mode, int(out_hr)))
         if self._profile:
             self.names.append(name)
+
+    def rot_amax_native(self, x: Tensor, x_stride: int, amax: Tensor, M: int, D: int, block: int, mode: int):
+        self._check(lib().h3b_rot_amax(self.ctx, x.ptr, _ABI_DTYPE[x.dtype], x_stride, amax.ptr, M, D, block, mode))
+        if self._profile:
+            self.names.append("rot_amax")
+
+    def rot_q8_given_amax_native(self, x: Tensor, x_stride: int, out: Tensor, amax_to_scale: Tensor, M: int, D: int,
+                                 block: int, mode: int):
+        self._check(lib().h3b_rot_q8_given_amax(self.ctx, x.ptr, _ABI_DTYPE[x.dtype], x_stride, out.ptr,
+                                                 amax_to_scale.ptr, M, D, block, mode))
+        if self._profile:
+            self.names.append("rot_q8_given_amax")
+
+    def dequant_native(self, acc: Tensor, acc_stride: int, sa: Tensor, sw: Tensor, bias: Tensor | None, out: Tensor,
+                       c_stride: int, M: int, N: int):
+        self._check(lib().h3b_dequant_i32(self.ctx, acc.ptr, acc_stride, sa.ptr, sw.ptr,
+                                           bias.ptr if bias is not None else None, out.ptr, _ABI_DTYPE[out.dtype],
+                                           c_stride, M, N))
+        if self._profile:
+            self.names.append("dequant")
 
     def gemm_native(self, a: Tensor, a_stride: int, w: Tensor, w_stride: int, sw: Tensor | None, sa: Tensor | None,
                     bias: Tensor | None, out: Tensor, out_dtype: str, c_stride: int, M: int, N: int, K: int,

@@ -1,0 +1,221 @@
+"""Sharding the quantised linears of a transformer block over the GPUs of one node.
+
+The reference is single-GPU; this module is new design on top of its operator API. One process per GPU
+(`torch.distributed`, NCCL over NVLink; gloo on CPU for the tests), three strategies:
+
+token-sharded   Rows are independent (per-token scales, per-row products), so each rank runs the whole layer on
+                M / p rows with replicated weights. No communication; bit-identical to one GPU.
+column-parallel W's rows (outputs) are split; activations are replicated; each rank produces its N / p columns.
+                Fused outputs are split PER SEGMENT (q | k | v, value | gate) so that a rank holds matching slices:
+                its value and gate columns line up for the swiglu rotate+quantise that feeds the next, row-parallel
+                layer. No communication; bit-identical per column.
+row-parallel    W's columns (K) are split; the input arrives already sharded on K (it is the previous
+                column-parallel layer's output). The reference quantises a token with ONE scale over the whole row
+                (kernels/ops.metal:315-317), so: (1) every rank rotates its shard and reports the row maxima,
+                (2) MAX all-reduce of M floats, (3) every rank quantises with the reduced maximum, (4) int8 product
+                into raw int32 accumulators, (5) SUM all-reduce of the int32 partials - integer addition is exact in
+                any order - (6) one epilogue (h3b_dequant_i32). Result: bit-identical to one GPU at any p. A faster,
+                approximate variant reduces dequantised fp32 or bf16 partials instead (`reduce="f32" | "bf16"`).
+                K / p must be a multiple of the rotation block. A LoRA term on a row-parallel layer is not supported.
+
+Collectives run on torch's current stream, which is also the stream the kernels are launched on, so a layer is
+one ordered sequence of kernels and collectives without host synchronisation.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+from . import ops
+from .gpu import Gpu, Tensor
+
+
+def _dist():
+    import torch.distributed as dist
+    return dist
+
+
+def shard_bounds(n: int, rank: int, world: int, multiple: int = 1):
+    """[start, stop) of rank's share of n items when n splits evenly into `world` pieces of a multiple of `multiple`."""
+    if n % (world * multiple):
+        raise ValueError(f"{n} does not split into {world} shards that are multiples of {multiple}")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def column_slices(N: int, splits, rank: int, world: int, multiple: int = 32):
+    """Row ranges of W [N][K] a rank owns under column parallelism: its 1/world share of every segment of `splits`
+    (default one segment = all of N), in segment order."""
+    splits = list(splits) if splits else [N]
+    if sum(splits) != N:
+        raise ValueError(f"segments {splits} do not add up to {N}")
+    out, base = [], 0
+    for seg in splits:
+        lo, hi = shard_bounds(seg, rank, world, multiple)
+        out.append((base + lo, base + hi))
+        base += seg
+    return out
+
+
+def take_rows(arr, slices):
+    """Concatenation of the row ranges `slices` of a NumPy array or torch tensor."""
+    if isinstance(arr, np.ndarray):
+        return np.ascontiguousarray(np.concatenate([arr[a:b] for a, b in slices], axis=0))
+    import torch
+    return torch.cat([arr[a:b] for a, b in slices], dim=0).contiguous()
+
+
+def _put(gpu, t):
+    if t is None:
+        return None
+    return gpu.upload(t) if isinstance(t, np.ndarray) else gpu.wrap(t)
+
+
+class TokenShardedLinear:
+    """The whole layer on this rank's rows [m0, m0 + rows) of M."""
+
+    def __init__(self, gpu: Gpu, group, wt: ops.QWeight, M: int, *, block: int = 128, swiglu_in: bool = False,
+                 out_dtype: str = "bf16"):
+        dist = _dist()
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.m0, m1 = shard_bounds(M, self.rank, self.world, 128)
+        self.rows = m1 - self.m0
+        self.gpu, self.wt, self.block, self.swiglu_in = gpu, wt, block, swiglu_in
+        self.a8 = gpu.empty((self.rows, wt.K), "i8")
+        self.sa = gpu.empty((self.rows,), "f32")
+        self.out = gpu.empty((self.rows, wt.N), out_dtype)
+
+    def __call__(self, x_local: Tensor) -> Tensor:
+        ops.rot_q8(self.gpu, x_local, self.a8, self.sa, self.rows, self.wt.K, swiglu=self.swiglu_in, block=self.block)
+        ops.gemm(self.gpu, self.a8, self.wt, self.out, self.rows, sa=self.sa, tile=(128, 32, 4))
+        return self.out
+
+
+class ColumnParallelLinear:
+    """This rank's N / p outputs of the layer; x is the full (replicated) activation."""
+
+    def __init__(self, gpu: Gpu, group, codes, scales, bias, M: int, *, block: int = 128, splits=None,
+                 swiglu_in: bool = False, out_dtype: str = "bf16", lora=None, scratch: ops.Scratch | None = None):
+        dist = _dist()
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        N, K = codes.shape
+        self.slices = column_slices(int(N), splits, self.rank, self.world)
+        low = None
+        if lora is not None:  # (A [r][K] in the rotated input space, B [N][r]): B's rows follow the weight's
+            A_l, B_l = lora
+            low = ops.low_rank(gpu, A_l, take_rows(B_l, self.slices), scratch or ops.Scratch(gpu))
+        self.wt = ops.QWeight("q8", _put(gpu, take_rows(codes, self.slices)), _put(gpu, take_rows(scales, self.slices)),
+                              sum(b - a for a, b in self.slices), int(K),
+                              bias=_put(gpu, take_rows(bias, self.slices)) if bias is not None else None, low=low)
+        self.gpu, self.M, self.block, self.swiglu_in = gpu, M, block, swiglu_in
+        self.m_pad = ops.pad_rows(M)
+        self.a8 = gpu.empty((self.m_pad, int(K)), "i8")
+        self.sa = gpu.empty((self.m_pad,), "f32")
+        self.out = gpu.empty((self.m_pad, self.wt.N), out_dtype)
+
+    def __call__(self, x: Tensor, x_stride: int | None = None) -> Tensor:
+        ops.rot_q8(self.gpu, x, self.a8, self.sa, self.M, self.wt.K, swiglu=self.swiglu_in, x_stride=x_stride,
+                   block=self.block)
+        ops.gemm(self.gpu, self.a8, self.wt, self.out, self.M, sa=self.sa, tile=(128, 32, 4))
+        return self.out
+
+
+class RowParallelLinear:
+    """The layer with K split over the ranks; x_local is this rank's K / p channels (2K / p holding value | gate with
+    swiglu_in). The output [M][N] is complete on every rank after the reduction."""
+
+    def __init__(self, gpu: Gpu, group, codes, scales, bias, M: int, *, block: int = 128, swiglu_in: bool = False,
+                 out_dtype: str = "bf16", reduce: str = "int32"):
+        dist = _dist()
+        if reduce not in ("int32", "f32", "bf16"):
+            raise ValueError(f"reduce={reduce!r}")
+        self.group, self.reduce = group, reduce
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        N, K = codes.shape
+        k0, k1 = shard_bounds(int(K), self.rank, self.world, block)
+        local = codes[:, k0:k1]
+        local = np.ascontiguousarray(local) if isinstance(local, np.ndarray) else local.contiguous()
+        self.wt = ops.QWeight("q8", _put(gpu, local), _put(gpu, scales), int(N), k1 - k0)
+        self.bias = _put(gpu, bias)
+        self.gpu, self.M, self.block, self.swiglu_in = gpu, M, block, swiglu_in
+        self.m_pad = ops.pad_rows(M)
+        self.a8 = gpu.empty((self.m_pad, k1 - k0), "i8")
+        self.sa = gpu.empty((self.m_pad,), "f32")
+        self.out = gpu.empty((self.m_pad, int(N)), out_dtype)
+        self.partial = gpu.empty((self.m_pad, int(N)), {"int32": "i32", "f32": "f32", "bf16": "bf16"}[reduce])
+        self._ones = None
+
+    def __call__(self, x_local: Tensor, x_stride: int | None = None) -> Tensor:
+        dist = _dist()
+        gpu, wt, M = self.gpu, self.wt, self.M
+        D = wt.K
+        stride = x_stride or (2 * D if self.swiglu_in else D)
+        mode = 1 if self.swiglu_in else 0
+        # (1)-(3): one scale per token over the WHOLE row
+        gpu.rot_amax_native(x_local, stride, self.sa, M, D, self.block, mode)
+        if self.world > 1:
+            dist.all_reduce(self.sa.torch(), op=dist.ReduceOp.MAX, group=self.group)
+        gpu.rot_q8_given_amax_native(x_local, stride, self.a8, self.sa, M, D, self.block, mode)
+        # (4)-(6)
+        if self.reduce == "int32":
+            ops.gemm(gpu, self.a8, wt, self.partial, M, sa=self.sa, tile=(128, 32, 4))  # i32 output: raw accumulators
+            if self.world > 1:
+                dist.all_reduce(self.partial.torch(), op=dist.ReduceOp.SUM, group=self.group)
+            gpu.dequant_native(self.partial, wt.N, self.sa, wt.sw, self.bias, self.out, wt.N, self.m_pad, wt.N)
+            return self.out
+        # approximate variants: dequantised partials are summed; the bias joins on rank 0 only
+        part_wt = ops.QWeight("q8", wt.w, wt.sw, wt.N, wt.K, bias=self.bias if self.rank == 0 else None)
+        ops.gemm(gpu, self.a8, part_wt, self.partial, M, sa=self.sa, tile=(128, 32, 4))
+        if self.world > 1:
+            dist.all_reduce(self.partial.torch(), op=dist.ReduceOp.SUM, group=self.group)
+        if self.partial.dtype == self.out.dtype:
+            return self.partial
+        self.out.torch().copy_(self.partial.torch())
+        return self.out
+
+
+class TensorParallelBlock:
+    """The four linears of a DiT block (QKV, attention-out, w1|w3, w2) sharded as column / row / column / row, with
+    synthetic weights drawn per rank on the device (timing only). Inputs that the model's attention and norm kernels
+    would produce (outside this path) are synthetic buffers of the right, sharded shapes."""
+
+    def __init__(self, gpu: Gpu, group, cfg, seed: int = 0, reduce: str = "int32"):
+        import torch
+        from . import workloads
+        dist = _dist()
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        gen = torch.Generator(device=gpu.torch_device)
+        gen.manual_seed(seed * 1000 + rank)
+        dev = gpu.torch_device
+        M, m_pad = cfg.M, ops.pad_rows(cfg.M)
+        self.gpu, self.cfg, self.layers, self.inputs = gpu, cfg, [], []
+        for spec in cfg.layers:
+            bias = torch.randn(spec.N, generator=gen, device=dev) * 0.01 if cfg.bias else None
+            if spec.parallel == "column":
+                # a rank only needs its own rows: draw them directly (N / world rows)
+                codes, scales = workloads.weight_torch(gen, spec.N // world, spec.K, dev)
+                layer = ColumnParallelLinear.__new__(ColumnParallelLinear)
+                layer.rank, layer.world, layer.slices = rank, world, [(0, spec.N // world)]
+                layer.wt = ops.QWeight("q8", gpu.wrap(codes), gpu.wrap(scales), spec.N // world, spec.K,
+                                       bias=gpu.wrap(bias[:spec.N // world].contiguous()) if bias is not None else None)
+                layer.gpu, layer.M, layer.block, layer.swiglu_in, layer.m_pad = gpu, M, cfg.block, spec.swiglu_in, m_pad
+                layer.a8, layer.sa = gpu.empty((m_pad, spec.K), "i8"), gpu.empty((m_pad,), "f32")
+                layer.out = gpu.empty((m_pad, spec.N // world), "bf16")
+                x = workloads.activations_torch(gen, m_pad, spec.K, cfg.n_outliers(spec.K), dev)
+                self.inputs.append(gpu.wrap(x))
+            else:
+                codes, scales = workloads.weight_torch(gen, spec.N, spec.K, dev)
+                layer = RowParallelLinear(gpu, group, codes, scales, bias, M, block=cfg.block,
+                                          swiglu_in=spec.swiglu_in, reduce=reduce)
+                if spec.swiglu_in:
+                    self.inputs.append(None)  # the previous (column-parallel) layer's local value | gate output
+                else:
+                    x = workloads.activations_torch(gen, m_pad, spec.K // world, cfg.n_outliers(spec.K // world), dev)
+                    self.inputs.append(gpu.wrap(x))
+            self.layers.append(layer)
+
+    def step(self):
+        prev = None
+        for layer, x in zip(self.layers, self.inputs):
+            prev = layer(prev if x is None else x)
+        return prev

@@ -72,6 +72,26 @@ H3B_API int h3b_use_own_stream(h3b_ctx *ctx);
 H3B_API int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, float *sa, int M, int D,
                int block, int mode, int out_hr);
 
+/* The two halves of h3b_rot_q8 for a row whose channels are sharded over several GPUs (a K-sharded, "row-parallel"
+ * layer): the reference quantises with ONE scale per token taken over the whole row (kernels/ops.metal:315-317), so
+ * each GPU first reports the largest rotated magnitude of its shard, the host reduces those with MAX over the GPUs,
+ * and each GPU then quantises its shard with the reduced value. No reference counterpart (single GPU).
+ *   h3b_rot_amax           amax[m] = max_c |rot(x)[m][c]| over this shard's D channels; writes no codes
+ *   h3b_rot_q8_given_amax  reads amax_to_scale[m] (the reduced maximum), writes the int8 codes of this shard and
+ *                          overwrites amax_to_scale[m] with the scale (amax / 127, or 1 for an all-zero row)
+ * Other arguments as h3b_rot_q8. With one shard the pair gives bit for bit what h3b_rot_q8 gives. */
+H3B_API int h3b_rot_amax(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, float *amax, int M, int D,
+                         int block, int mode);
+H3B_API int h3b_rot_q8_given_amax(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out,
+                                  float *amax_to_scale, int M, int D, int block, int mode);
+
+/* The product's epilogue on its own: C[m][n] = c_dtype(float(acc[m][n]) * sa[m] * sw[n] + bias[n]) for int32
+ * accumulators [M][acc_stride] produced by h3b_gemm_w8a8 with H3B_I32 and summed over the GPUs of a K-sharded layer.
+ * Same operation order as the fused epilogue (kernels/gemm.metal:238-255), so the result equals the single-GPU
+ * product bit for bit. No reference counterpart. */
+H3B_API int h3b_dequant_i32(h3b_ctx *ctx, const int32_t *acc, int64_t acc_stride, const float *sa, const float *sw,
+                            const float *bias, void *C, int c_dtype, int64_t c_stride, int M, int N);
+
 /* int8 x int8 product with the dequantising epilogue. Replaces the dispatch of the Metal kernel gemm with weight
  * format 1 and epilogue 0 (kernels/gemm.metal:117-261; parameter block GemmParams kernels/params.h:7-16; launcher
  * h3metal/ops.py:124-174; buffer order a, w, sw, sa, out, bias, ..., lt, lb, lr).

@@ -58,3 +58,73 @@ class RecordingGpu:
     def rot_q8_native(self, x, x_stride, out, sa, M, D, block, mode, out_hr, name="rot_q8"):
         self.calls.append(dict(kind="rot_q8", x=x, x_stride=x_stride, out=out, sa=sa, M=M, D=D, block=block,
                                mode=mode, out_hr=out_hr))
+
+
+def _host_torch(self):
+    """The same host memory as a torch CPU tensor (so that gloo collectives act on it in place)."""
+    import torch
+    arr = self.numpy()
+    if self.dtype == "bf16":
+        return torch.from_numpy(arr.view(np.int16)).view(torch.bfloat16)
+    return torch.from_numpy(arr)
+
+
+HostTensor.torch = _host_torch
+
+
+class OracleBackedGpu(RecordingGpu):
+    """Executes the native calls with the CPU oracle, on host arrays. Lets the multi-rank orchestration of
+    h3metal_b200.parallel run under gloo without a GPU; the arithmetic is the oracle's, the sequencing (which
+    shard, which collective, which epilogue) is the product's."""
+
+    def _rows(self, t, rows, cols, stride, dtype):
+        flat = t.buf.arr.view(np.uint8).reshape(-1)[t.offset:].view(gpu_mod._NP[dtype])[:(rows - 1) * stride + cols]
+        return np.lib.stride_tricks.as_strided(flat, (rows, cols), (stride * flat.itemsize, flat.itemsize))
+
+    def _rotated(self, x, x_stride, M, D, block, mode):
+        from oracle import rotq8_ref
+        cols = 2 * D if mode == 1 else D
+        mat = self._rows(x, M, cols, x_stride, x.dtype)
+        xf = rotq8_ref._as_f32_input(mat, x.dtype)
+        val = xf[:, :D]
+        if mode == 1:
+            val = (val * rotq8_ref.silu_f32(xf[:, D:2 * D])).astype(np.float32)
+        return (rotq8_ref.fwht_blocks_f32(val, block) * rotq8_ref.normaliser(block)).astype(np.float32)
+
+    def rot_q8_native(self, x, x_stride, out, sa, M, D, block, mode, out_hr, name="rot_q8"):
+        v = self._rotated(x, x_stride, M, D, block, mode)
+        amax = np.abs(v).max(axis=1)
+        self._quantise(v, amax, out, sa, M, D)
+
+    def rot_amax_native(self, x, x_stride, amax, M, D, block, mode):
+        amax.numpy().reshape(-1)[:M] = np.abs(self._rotated(x, x_stride, M, D, block, mode)).max(axis=1)
+
+    def rot_q8_given_amax_native(self, x, x_stride, out, amax_to_scale, M, D, block, mode):
+        v = self._rotated(x, x_stride, M, D, block, mode)
+        self._quantise(v, amax_to_scale.numpy().reshape(-1)[:M].copy(), out, amax_to_scale, M, D)
+
+    def _quantise(self, v, amax, out, sa, M, D):
+        scale = np.where(amax > 0, amax / np.float32(127.0), np.float32(1.0)).astype(np.float32)
+        rs = (np.float32(1.0) / scale).astype(np.float32)
+        q = np.rint((v * rs[:, None]).astype(np.float32)).astype(np.int32).astype(np.int8)
+        self._rows(out, M, D, D, "i8")[...] = q
+        sa.numpy().reshape(-1)[:M] = scale
+
+    def gemm_native(self, a, a_stride, w, w_stride, sw, sa, bias, out, out_dtype, c_stride, M, N, K, lt=None,
+                    t_stride=0, lb=None, b_stride=0, R=0, ranges_ptr=None, name="gemm"):
+        from oracle import gemm_ref
+        assert lt is None, "the fake does not carry the low-rank term"
+        acc = gemm_ref.int32_product(self._rows(a, M, K, a_stride, "i8"), self._rows(w, N, K, w_stride, "i8"))
+        dst = self._rows(out, M, N, c_stride, out_dtype)
+        if out_dtype == "i32":
+            dst[...] = acc
+            return
+        v = gemm_ref.epilogue_q8(acc, sa.numpy().reshape(-1)[:M], sw.numpy().reshape(-1)[:N],
+                                 bias.numpy().reshape(-1)[:N] if bias is not None else None)
+        dst[...] = gemm_ref.store_as(v, out_dtype)
+
+    def dequant_native(self, acc, acc_stride, sa, sw, bias, out, c_stride, M, N):
+        from oracle import gemm_ref
+        v = gemm_ref.epilogue_q8(self._rows(acc, M, N, acc_stride, "i32"), sa.numpy().reshape(-1)[:M],
+                                 sw.numpy().reshape(-1)[:N], bias.numpy().reshape(-1)[:N] if bias is not None else None)
+        self._rows(out, M, N, c_stride, out.dtype)[...] = gemm_ref.store_as(v, out.dtype)

@@ -1,0 +1,76 @@
+"""Two GPUs, one process each, NCCL: the sharded layers of h3metal_b200.parallel against the single-GPU result.
+Skipped on a box with one GPU (the CPU suite covers the orchestration with gloo)."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r'''
+import os, sys
+import numpy as np
+import torch, torch.distributed as dist
+sys.path.insert(0, os.environ["H3B_ROOT"])
+import oracle
+from oracle import gemm_ref
+from h3metal_b200 import ops, parallel
+from h3metal_b200.gpu import Gpu
+
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+g = Gpu(device=rank)
+M, D, F, B = 384, 1024, 2048, 128
+rng = np.random.default_rng(5)
+x = oracle.bf16_round_bits((rng.standard_normal((M, D)) * 2).astype(np.float32))
+w_up = rng.integers(-127, 128, size=(2 * F, D), dtype=np.int8); s_up = rng.uniform(1e-3, 2e-3, size=2 * F).astype(np.float32)
+b_up = (rng.standard_normal(2 * F) * 0.01).astype(np.float32)
+w_dn = rng.integers(-127, 128, size=(D, F), dtype=np.int8); s_dn = rng.uniform(1e-3, 2e-3, size=D).astype(np.float32)
+b_dn = (rng.standard_normal(D) * 0.01).astype(np.float32)
+up = parallel.ColumnParallelLinear(g, None, w_up, s_up, b_up, M, block=B, splits=[F, F])
+down = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=B, swiglu_in=True)
+h_local = up(g.upload(x, "bf16"))
+y = down(h_local)
+g.wait()
+# single-GPU result with the same kernels
+full_up = ops.QWeight("q8", g.upload(w_up), g.upload(s_up), 2 * F, D, bias=g.upload(b_up))
+full_dn = ops.QWeight("q8", g.upload(w_dn), g.upload(s_dn), D, F, bias=g.upload(b_dn))
+a8, sa, h = g.empty((M, D), "i8"), g.empty((M,), "f32"), g.empty((M, 2 * F), "bf16")
+ops.rot_q8(g, g.upload(x, "bf16"), a8, sa, M, D, block=B); ops.gemm(g, a8, full_up, h, M, sa=sa, tile=(128, 32, 4))
+a8b, sab, y1 = g.empty((M, F), "i8"), g.empty((M,), "f32"), g.empty((M, D), "bf16")
+ops.rot_q8(g, h, a8b, sab, M, F, swiglu=True, block=B); ops.gemm(g, a8b, full_dn, y1, M, sa=sab, tile=(128, 32, 4))
+g.wait()
+hh = h.numpy(); want_local = np.concatenate([hh[:, a:b] for a, b in up.slices], axis=1)
+assert np.array_equal(h_local.numpy(), want_local), "column-parallel output"
+assert np.array_equal(down.sa.numpy(), sab.numpy()), "whole-row scales"
+half = F // world
+assert np.array_equal(down.a8.numpy(), a8b.numpy()[:, rank * half:(rank + 1) * half]), "K-shard codes"
+assert np.array_equal(y.numpy(), y1.numpy()), "row-parallel output"
+dist.barrier(); dist.destroy_process_group()
+print(f"rank {rank} ok")
+'''
+
+
+def test_two_gpus_match_one_gpu_bit_for_bit(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), H3B_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for rank, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"rank {rank} ok" in out, out[-2000:]

@@ -1,0 +1,103 @@
+"""Multi-rank orchestration of h3metal_b200.parallel on CPU: two gloo ranks, kernels replaced by the oracle
+(tests/fakes.py: OracleBackedGpu). Checks the sharding plans and that every strategy reproduces the single-rank
+result bit for bit (row-parallel: whole-row scales through the MAX all-reduce, exact int32 SUM all-reduce)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from oracle import gemm_ref
+from h3metal_b200 import parallel
+
+WORLD = 2
+M, D, F, BLOCK = 256, 512, 1024, 128
+
+
+def test_shard_plans():
+    assert parallel.shard_bounds(1024, 1, 4, 128) == (256, 512)
+    with pytest.raises(ValueError):
+        parallel.shard_bounds(1000, 0, 4, 128)
+    # q | k | v fused output: each rank takes its share of every third
+    assert parallel.column_slices(3 * 512, [512, 512, 512], 1, 2) == [(256, 512), (768, 1024), (1280, 1536)]
+    # value | gate: matching halves
+    assert parallel.column_slices(2 * 1024, [1024, 1024], 0, 2) == [(0, 512), (1024, 1536)]
+    with pytest.raises(ValueError):
+        parallel.column_slices(100, [60, 30], 0, 2)
+    a = np.arange(12).reshape(6, 2)
+    assert parallel.take_rows(a, [(0, 1), (4, 6)]).tolist() == [[0, 1], [8, 9], [10, 11]]
+
+
+def _inputs():
+    rng = np.random.default_rng(7)
+    x = oracle.bf16_round_bits((rng.standard_normal((M, D)) * 2).astype(np.float32))
+    w_up = rng.integers(-127, 128, size=(2 * F, D), dtype=np.int8)       # value | gate, column-parallel
+    s_up = rng.uniform(1e-3, 2e-3, size=2 * F).astype(np.float32)
+    b_up = (rng.standard_normal(2 * F) * 0.01).astype(np.float32)
+    w_dn = rng.integers(-127, 128, size=(D, F), dtype=np.int8)           # row-parallel, fed by swiglu
+    s_dn = rng.uniform(1e-3, 2e-3, size=D).astype(np.float32)
+    b_dn = (rng.standard_normal(D) * 0.01).astype(np.float32)
+    return x, (w_up, s_up, b_up), (w_dn, s_dn, b_dn)
+
+
+def _single_rank_reference():
+    x, (w_up, s_up, b_up), (w_dn, s_dn, b_dn) = _inputs()
+    q, s = oracle.rot_q8_rows(x, D, block=BLOCK)
+    h, _, _ = gemm_ref.gemm_q8(q, w_up, s, s_up, b_up, None, "bf16")
+    q2, s2 = oracle.rot_q8_rows(h, F, block=BLOCK, swiglu=True)
+    y, _, acc = gemm_ref.gemm_q8(q2, w_dn, s2, s_dn, b_dn, None, "bf16")
+    return h, q2, s2, y
+
+
+def _worker(rank, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        from tests.fakes import OracleBackedGpu
+        g = OracleBackedGpu()
+        x, (w_up, s_up, b_up), (w_dn, s_dn, b_dn) = _inputs()
+        up = parallel.ColumnParallelLinear(g, None, w_up, s_up, b_up, M, block=BLOCK, splits=[F, F])
+        down = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True)
+        h_local = up(g.upload(x, "bf16"))
+        y = down(h_local)
+        down_f32 = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True, reduce="f32")
+        y_fast = down_f32(h_local)
+        tok = parallel.TokenShardedLinear(g, None, parallel.ops.QWeight("q8", g.upload(w_up), g.upload(s_up), 2 * F, D,
+                                                                         bias=g.upload(b_up)), M, block=BLOCK)
+        h_tok = tok(g.upload(x[tok.m0:tok.m0 + tok.rows], "bf16"))
+        results[rank] = dict(slices=up.slices, h_local=h_local.numpy().copy(), a8=down.a8.numpy().copy(),
+                             sa=down.sa.numpy().copy(), y=y.numpy().copy(), y_fast=y_fast.numpy().copy(),
+                             tok=(tok.m0, tok.rows, h_tok.numpy().copy()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_reproduce_one_rank_bit_for_bit():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    results = mp.Manager().dict()
+    mp.spawn(_worker, args=(port, results), nprocs=WORLD, join=True)
+    h, q2, s2, y = _single_rank_reference()
+    half = F // WORLD
+    for rank in range(WORLD):
+        r = results[rank]
+        # column-parallel: this rank's value and gate slices, side by side
+        assert r["slices"] == [(rank * half, (rank + 1) * half), (F + rank * half, F + (rank + 1) * half)]
+        want_local = np.concatenate([h[:, a:b] for a, b in r["slices"]], axis=1)
+        assert np.array_equal(r["h_local"], want_local)
+        # row-parallel: codes of this K shard quantised with the WHOLE row's scale; exact output on every rank
+        assert np.array_equal(r["a8"], q2[:, rank * half:(rank + 1) * half])
+        assert np.array_equal(r["sa"], s2)
+        assert np.array_equal(r["y"], y)
+        # approximate variant (fp32 partials): inside the path's 1e-3 bound
+        got = oracle.bf16_bits_to_f32(r["y_fast"]).astype(np.float64)
+        want = oracle.bf16_bits_to_f32(y).astype(np.float64)
+        assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
+        # token-sharded: rows of the full result
+        m0, rows, h_tok = r["tok"]
+        assert (m0, rows) == (rank * M // WORLD, M // WORLD) and np.array_equal(h_tok, h[m0:m0 + rows])
