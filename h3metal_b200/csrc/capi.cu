@@ -80,7 +80,8 @@ struct h3b_ctx {
   int *status_host = nullptr;  // pinned copy read at wait
   EncodeTiledFn encode = nullptr;
   std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
-  int tile_n_override = 0, band_override = 0, rot_threads = 0, rot_stages = 0;
+  int tile_n_override = 0, band_override = 0, pair_mode = 0, rot_threads = 0, rot_stages = 0;
+  int pair_stages = 0, pair_clusters = 0;  // CTA-pair product: ring depth and resident clusters (0 = unavailable)
   uint64_t launches = 0;
   std::string name;
 
@@ -227,6 +228,10 @@ h3b_ctx *h3b_open(int device) {
   }
   ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
   if ((e = h3b::gemm_configure(device)) != cudaSuccess) return bail("cudaFuncSetAttribute(max dynamic shared memory)", e);
+  if ((e = h3b::gemm_pair_configure()) != cudaSuccess) return bail("cudaFuncSetAttribute(max dynamic shared memory)", e);
+  ctx->pair_stages = h3b::gemm_pair_pick_stages(ctx->prop.sharedMemPerBlockOptin);
+  ctx->pair_clusters = ctx->pair_stages >= 2 ? h3b::gemm_pair_max_clusters(ctx->pair_stages) : 0;
+  cudaGetLastError();  // an occupancy query that failed must not poison the next launch check
   return ctx;
 }
 
@@ -335,8 +340,10 @@ int h3b_dequant_i32(h3b_ctx *ctx, const int32_t *acc, int64_t acc_stride, const 
   return ctx->after_launch("dequant launch", e);
 }
 
-int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band) {
+int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band, int pair) {
   if (!ctx) return fail("null context");
+  if (pair < -1 || pair > 1) return fail("gemm policy: pair must be -1 (never), 0 (automatic) or 1 (whenever possible)");
+  ctx->pair_mode = pair;
   if (tile_n != 0 && tile_n != 32 && tile_n != 64 && tile_n != 128 && tile_n != 256)
     return fail("gemm policy: tile_n must be 0, 32, 64, 128 or 256");
   if (band < 0) return fail("gemm policy: band must be >= 0");
@@ -380,8 +387,12 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
         (b_stride * 2) % 16)
       return fail("gemm: T and B must be 16-byte aligned with row strides that are multiples of 16 bytes");
   }
-  const int bn = h3b_gemm_tile_n(ctx, N, lora);
-  const int stages = h3b::gemm_pick_stages(bn, lora ? R : 0, ctx->prop.sharedMemPerBlockOptin);
+  // Single CTAs (128 x tile_n tiles) by default. CTA pairs (256 x 256 tiles, B operand shared across the pair) are
+  // available on request: measured on B200 they match the single-CTA kernel at the models' shapes and trail it on the
+  // largest ones, the product being limited by the board's power cap rather than by shared-memory traffic.
+  const bool pair = !lora && ctx->pair_clusters > 0 && ctx->pair_mode == 1 && !ctx->tile_n_override;
+  const int bn = pair ? 128 : h3b_gemm_tile_n(ctx, N, lora);  // rows of W one CTA stages per K block
+  const int stages = pair ? ctx->pair_stages : h3b::gemm_pick_stages(bn, lora ? R : 0, ctx->prop.sharedMemPerBlockOptin);
   if (stages < 2) return fail("gemm: tile does not fit the device's shared memory");
 
   h3b::GemmLaunch g;
@@ -401,22 +412,28 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
   g.sw = sw; g.sa = sa; g.bias = raw ? nullptr : bias; g.c = C; g.ranges = lora ? lora_ranges : nullptr;
   g.c_stride = c_stride; g.c_dtype = c_dtype; g.M = M; g.N = N; g.K = K; g.R = lora ? R : 0; g.bn = bn;
   g.acc_stages = (lora && bn == 256) ? 1 : 2;
-  const int m_tiles = (M + 127) / 128, n_tiles = (N + bn - 1) / bn;
+  const int tile_m = pair ? 256 : 128, tile_n = pair ? 256 : bn;
+  const int m_tiles = (M + tile_m - 1) / tile_m, n_tiles = (N + tile_n - 1) / tile_n;
   int band = ctx->band_override;
   if (band <= 0) {
-    // keep the A band (band x 128 rows x K bytes) well inside L2 while W streams through once per band
+    // keep the A band (band x tile_m rows x K bytes) well inside L2 while W streams through once per band
     const long long budget = 24LL << 20;
-    band = static_cast<int>(budget / (128LL * K));
-    if (band < 4) band = 4;
+    band = static_cast<int>(budget / (static_cast<long long>(tile_m) * K));
+    if (band < (pair ? 2 : 4)) band = pair ? 2 : 4;
   }
   if (band > m_tiles) band = m_tiles;
   g.band = band;
   const long long tiles = static_cast<long long>(m_tiles) * n_tiles;
-  g.grid = static_cast<int>(tiles < ctx->prop.multiProcessorCount ? tiles : ctx->prop.multiProcessorCount);
   g.status = ctx->status_dev;
 
   cudaEvent_t ps = nullptr;
   if (ctx->before_launch(&ps)) return -1;
+  if (pair) {
+    const int clusters = static_cast<int>(tiles < ctx->pair_clusters ? tiles : ctx->pair_clusters);
+    g.grid = 2 * clusters;
+    return ctx->after_launch("gemm launch", h3b::launch_gemm_w8a8_pair(g, stages, clusters, ctx->stream));
+  }
+  g.grid = static_cast<int>(tiles < ctx->prop.multiProcessorCount ? tiles : ctx->prop.multiProcessorCount);
   const cudaError_t e = h3b::launch_gemm_w8a8(g, stages, ctx->stream);
   return ctx->after_launch("gemm launch", e);
 }

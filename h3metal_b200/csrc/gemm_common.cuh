@@ -1,0 +1,153 @@
+// Pieces shared by the single-CTA and the CTA-pair product kernels: tile constants, the persistent tile order, the
+// conversion and packing of output values, and the per-chunk epilogue in the reference's operation order
+// (kernels/gemm.metal:238-255 of the reference).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace h3b {
+namespace gemm {
+
+constexpr int kBM = 128;            // rows per tile = MMA M
+constexpr int kBKBytes = 128;       // K bytes per stage row = one 128-byte swizzle span
+constexpr int kABytes = kBM * kBKBytes;
+constexpr int kMaxStages = 8;
+constexpr int kLoraChunk = 32;      // ranks per LoRA shared-memory chunk: 32 halves = one 64-byte swizzle span
+constexpr int kLoraTBytes = kBM * kLoraChunk * 2;
+constexpr int kTmemCols = 512;
+constexpr int kLowBase = 256;       // first TMEM column of the LoRA accumulators
+constexpr int kThreads = 192;
+constexpr int kBarrierBytes = 256;
+
+__host__ __device__ constexpr int stage_bytes(int bn) { return kABytes + bn * kBKBytes; }
+__host__ __device__ constexpr int lora_bytes(int bn, int R) { return (R / kLoraChunk) * (kLoraTBytes + bn * kLoraChunk * 2); }
+
+struct TileCoord {
+  int m_blk, n_blk;
+};
+
+// Tile t of the persistent schedule: bands of `band` row tiles; inside a band row tiles vary fastest.
+__device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_tiles, int band) {
+  const int per_band = band * n_tiles;
+  const int b = t / per_band;
+  const int rows = min(band, m_tiles - b * band);
+  const int r = t - b * per_band;
+  TileCoord c;
+  c.m_blk = b * band + r % rows;
+  c.n_blk = r / rows;
+  return c;
+}
+
+template <typename OUT_T>
+__device__ __forceinline__ OUT_T to_out(float v);
+template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// 32 consecutive values of one row, converted to OUT_T and packed into 32-bit words (16 words for 2-byte types).
+template <typename OUT_T>
+struct Packed;
+template <>
+struct Packed<float> {
+  static constexpr int kWords = 32;
+  static __device__ __forceinline__ void pack(const float (&v)[32], uint32_t (&w)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(v[j]);
+  }
+};
+template <>
+struct Packed<__half> {
+  static constexpr int kWords = 16;
+  static __device__ __forceinline__ void pack(const float (&v)[32], uint32_t (&w)[32]) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+  }
+};
+template <>
+struct Packed<__nv_bfloat16> {
+  static constexpr int kWords = 16;
+  static __device__ __forceinline__ void pack(const float (&v)[32], uint32_t (&w)[32]) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+  }
+};
+
+// Stores 32 consecutive output values of one row; 16-byte vector stores when the segment is aligned and whole.
+template <typename OUT_T>
+__device__ __forceinline__ void store_segment(OUT_T *dst, const float (&v)[32], int n_valid, bool vec_ok) {
+  if (vec_ok && n_valid >= 32) {
+    uint32_t w[32];
+    Packed<OUT_T>::pack(v, w);
+#pragma unroll
+    for (int j = 0; j < Packed<OUT_T>::kWords / 4; ++j)
+      reinterpret_cast<uint4 *>(dst)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < n_valid) dst[j] = to_out<OUT_T>(v[j]);
+    }
+  }
+}
+
+// Finishes 32 accumulator columns [n, n + 32) of row m: either the raw int32 values, or the dequantising
+// epilogue float(acc) * sa * sw (+ bias) (+ low) in the reference's operation order, converted to the output type.
+// sw_s / bias_s point at the tile's staged column scales and biases for these 32 columns.
+__device__ __forceinline__ void finish_chunk(const GemmLaunch &g, const uint32_t (&acc)[32], const uint32_t (&low)[32],
+                                             bool has_low, int m, int n, float sa_m, const float *sw_s,
+                                             const float *bias_s, bool vec_ok) {
+  const int n_valid = g.N - n;
+  if (m >= g.M || n_valid <= 0) return;
+  if (g.c_dtype == kDtypeI32) {
+    int32_t *dst = static_cast<int32_t *>(g.c) + static_cast<size_t>(m) * g.c_stride + n;
+    if (vec_ok && n_valid >= 32) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        reinterpret_cast<uint4 *>(dst)[j] = make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < n_valid) dst[j] = static_cast<int32_t>(acc[j]);
+      }
+    }
+    return;
+  }
+  const bool has_bias = g.bias != nullptr;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float x = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(acc[j])), sa_m), sw_s[j]);
+    if (has_bias) x = __fadd_rn(x, bias_s[j]);
+    if (has_low) x = __fadd_rn(x, __uint_as_float(low[j]));
+    v[j] = x;
+  }
+  const size_t off = static_cast<size_t>(m) * g.c_stride + n;
+  if (g.c_dtype == kDtypeBf16) store_segment(static_cast<__nv_bfloat16 *>(g.c) + off, v, n_valid, vec_ok);
+  else if (g.c_dtype == kDtypeF16) store_segment(static_cast<__half *>(g.c) + off, v, n_valid, vec_ok);
+  else store_segment(static_cast<float *>(g.c) + off, v, n_valid, vec_ok);
+}
+
+// Stages the column scales and biases of columns [n0, n0 + bn) in a warp's own slice of shared memory.
+__device__ __forceinline__ void stage_columns(const GemmLaunch &g, int n0, int bn, int lane, float *sw_s, float *bias_s) {
+  __syncwarp();
+  if (g.c_dtype != kDtypeI32) {
+    for (int j = lane; j < bn; j += 32) {
+      const int n = n0 + j;
+      sw_s[j] = n < g.N ? __ldg(g.sw + n) : 0.0f;
+      bias_s[j] = (g.bias != nullptr && n < g.N) ? __ldg(g.bias + n) : 0.0f;
+    }
+  }
+  __syncwarp();
+}
+
+}  // namespace gemm
+}  // namespace h3b

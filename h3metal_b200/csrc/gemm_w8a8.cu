@@ -26,98 +26,12 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include "kernels.h"
-#include "ptx.cuh"
+#include "gemm_common.cuh"
 
 namespace h3b {
 namespace {
 
-constexpr int kBM = 128;            // rows per tile = MMA M
-constexpr int kBKBytes = 128;       // K bytes per stage row = one 128-byte swizzle span
-constexpr int kABytes = kBM * kBKBytes;
-constexpr int kMaxStages = 8;
-constexpr int kLoraChunk = 32;      // ranks per LoRA shared-memory chunk: 32 halves = one 64-byte swizzle span
-constexpr int kLoraTBytes = kBM * kLoraChunk * 2;
-constexpr int kTmemCols = 512;
-constexpr int kLowBase = 256;       // first TMEM column of the LoRA accumulators
-constexpr int kThreads = 192;
-constexpr int kBarrierBytes = 256;
-
-__host__ __device__ constexpr int stage_bytes(int bn) { return kABytes + bn * kBKBytes; }
-__host__ __device__ constexpr int lora_bytes(int bn, int R) { return (R / kLoraChunk) * (kLoraTBytes + bn * kLoraChunk * 2); }
-
-struct TileCoord {
-  int m_blk, n_blk;
-};
-
-// Tile t of the persistent schedule: bands of `band` row tiles; inside a band row tiles vary fastest.
-__device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_tiles, int band) {
-  const int per_band = band * n_tiles;
-  const int b = t / per_band;
-  const int rows = min(band, m_tiles - b * band);
-  const int r = t - b * per_band;
-  TileCoord c;
-  c.m_blk = b * band + r % rows;
-  c.n_blk = r / rows;
-  return c;
-}
-
-template <typename OUT_T>
-__device__ __forceinline__ OUT_T to_out(float v);
-template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
-template <> __device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
-template <> __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
-
-// 32 consecutive values of one row, converted to OUT_T and packed into 32-bit words (16 words for 2-byte types).
-template <typename OUT_T>
-struct Packed;
-template <>
-struct Packed<float> {
-  static constexpr int kWords = 32;
-  static __device__ __forceinline__ void pack(const float (&v)[32], uint32_t (&w)[32]) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(v[j]);
-  }
-};
-template <>
-struct Packed<__half> {
-  static constexpr int kWords = 16;
-  static __device__ __forceinline__ void pack(const float (&v)[32], uint32_t (&w)[32]) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-      w[j] = *reinterpret_cast<const uint32_t *>(&h);
-    }
-  }
-};
-template <>
-struct Packed<__nv_bfloat16> {
-  static constexpr int kWords = 16;
-  static __device__ __forceinline__ void pack(const float (&v)[32], uint32_t (&w)[32]) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-      w[j] = *reinterpret_cast<const uint32_t *>(&h);
-    }
-  }
-};
-
-// Stores 32 consecutive output values of one row; 16-byte vector stores when the segment is aligned and whole.
-template <typename OUT_T>
-__device__ __forceinline__ void store_segment(OUT_T *dst, const float (&v)[32], int n_valid, bool vec_ok) {
-  if (vec_ok && n_valid >= 32) {
-    uint32_t w[32];
-    Packed<OUT_T>::pack(v, w);
-#pragma unroll
-    for (int j = 0; j < Packed<OUT_T>::kWords / 4; ++j)
-      reinterpret_cast<uint4 *>(dst)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (j < n_valid) dst[j] = to_out<OUT_T>(v[j]);
-    }
-  }
-}
+using namespace gemm;
 
 template <int BN, int ACC_STAGES, bool LORA>
 __global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_constant__ GemmLaunch g,
@@ -292,15 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_con
       const uint32_t aph = (at / ACC_STAGES) & 1u;
       // per-column scale and bias of this tile -> this warp's own slice of shared memory (no cross-warp barrier)
       float *sw_s = col_stage + quarter * 2 * BN, *bias_s = sw_s + BN;
-      __syncwarp();
-      if (!raw) {
-        for (int j = lane; j < BN; j += 32) {
-          const int n = n0 + j;
-          sw_s[j] = n < g.N ? __ldg(g.sw + n) : 0.0f;
-          bias_s[j] = (g.bias != nullptr && n < g.N) ? __ldg(g.bias + n) : 0.0f;
-        }
-      }
-      __syncwarp();
+      stage_columns(g, n0, BN, lane, sw_s, bias_s);
       const int m = m0 + row;
       const float sa_m = (!raw && m < g.M) ? __ldg(g.sa + m) : 0.0f;
       bool has_low = false;
@@ -317,7 +223,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_con
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN;
       const uint32_t t_low = t_acc + kLowBase;
-      const bool has_bias = g.bias != nullptr;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t acc[32];
@@ -325,36 +230,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_con
         tmem_ld_32x32b_x32(t_acc + c * 32, acc);
         if (LORA && has_low) tmem_ld_32x32b_x32(t_low + c * 32, low);
         tmem_ld_wait();
-        const int n = n0 + c * 32;
-        const int n_valid = g.N - n;
-        if (m < g.M && n_valid > 0) {
-          if (raw) {
-            int32_t *dst = static_cast<int32_t *>(g.c) + static_cast<size_t>(m) * g.c_stride + n;
-            if (vec_ok && n_valid >= 32) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                reinterpret_cast<uint4 *>(dst)[j] = make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (j < n_valid) dst[j] = static_cast<int32_t>(acc[j]);
-              }
-            }
-          } else {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float x = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(acc[j])), sa_m), sw_s[c * 32 + j]);
-              if (has_bias) x = __fadd_rn(x, bias_s[c * 32 + j]);
-              if (LORA && has_low) x = __fadd_rn(x, __uint_as_float(low[j]));
-              v[j] = x;
-            }
-            const size_t off = static_cast<size_t>(m) * g.c_stride + n;
-            if (g.c_dtype == kDtypeBf16) store_segment(static_cast<__nv_bfloat16 *>(g.c) + off, v, n_valid, vec_ok);
-            else if (g.c_dtype == kDtypeF16) store_segment(static_cast<__half *>(g.c) + off, v, n_valid, vec_ok);
-            else store_segment(static_cast<float *>(g.c) + off, v, n_valid, vec_ok);
-          }
-        }
+        finish_chunk(g, acc, low, LORA && has_low, m, n0 + c * 32, sa_m, sw_s + c * 32, bias_s + c * 32, vec_ok);
       }
       tc_fence_before_sync();
       __syncwarp();

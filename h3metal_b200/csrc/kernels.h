@@ -60,4 +60,12 @@ int gemm_pick_stages(int bn, int R, size_t smem_optin);
 cudaError_t gemm_configure(int device);  // raises the dynamic shared-memory limit of every instantiation
 cudaError_t launch_gemm_w8a8(const GemmLaunch &g, int stages, cudaStream_t stream);
 
+// CTA-pair variant (256 x 256 tile per cluster of two CTAs, no low-rank term). map_w must have a box of 128 rows
+// (each CTA stages half of the W tile); g.band counts 256-row tiles; g.bn is ignored.
+size_t gemm_pair_smem_bytes(int stages);
+int gemm_pair_pick_stages(size_t smem_optin);
+cudaError_t gemm_pair_configure();
+int gemm_pair_max_clusters(int stages);
+cudaError_t launch_gemm_w8a8_pair(const GemmLaunch &g, int stages, int clusters, cudaStream_t stream);
+
 }  // namespace h3b

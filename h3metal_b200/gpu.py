@@ -69,7 +69,7 @@ def _signatures():
         "h3b_gemm_w8a8_lora_noalloc": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32, i32, vp, i64, vp,
                                              vp, i64, i32, vp]),
         "h3b_gemm_tile_n": (i32, [vp, i32, i32]),
-        "h3b_gemm_set_policy": (i32, [vp, i32, i32]),
+        "h3b_gemm_set_policy": (i32, [vp, i32, i32, i32]),
         "h3b_rot_set_policy": (i32, [vp, i32, i32]),
         "h3b_commit": (None, [vp]),
         "h3b_wait": (dbl, [vp]),
@@ -316,10 +316,11 @@ class Gpu:
     def gemm_tile_n(self, N: int, lora: bool) -> int:
         return lib().h3b_gemm_tile_n(self.ctx, N, int(lora))
 
-    def set_policy(self, tile_n: int = 0, band: int = 0, rot_threads: int = 0, rot_stages: int = 0):
+    def set_policy(self, tile_n: int = 0, band: int = 0, rot_threads: int = 0, rot_stages: int = 0, pair: int = 0):
         """Overrides of the library's own choices (0 = automatic), for tuning sweeps and for tests that want a
-        particular kernel variant. rot_stages = -1 selects the register-fed rotate+quantise kernel."""
-        self._check(lib().h3b_gemm_set_policy(self.ctx, tile_n, band))
+        particular kernel variant. rot_stages = -1 selects the register-fed rotate+quantise kernel; pair = -1 / 1 keeps
+        the product off / on CTA pairs."""
+        self._check(lib().h3b_gemm_set_policy(self.ctx, tile_n, band, pair))
         self._check(lib().h3b_rot_set_policy(self.ctx, rot_threads, rot_stages))
 
     # -- execution ------------------------------------------------------------------------------------------------

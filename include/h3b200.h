@@ -142,9 +142,11 @@ H3B_API int h3b_gemm_w8a8_lora_noalloc(h3b_ctx *ctx, const int8_t *A, int64_t a_
 /* Column-tile width the product uses for N outputs with (lora != 0) or without a low-rank term: the granularity
  * of lora_ranges. Plays the part of the TN macro the reference compiles into its kernel (kernels/gemm.metal:48-50). */
 H3B_API int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int lora);
-/* Overrides the product's choices: tile_n (0 = automatic; 32, 64, 128, 256) and band (row tiles swept per column
- * tile, 0 = automatic). The counterpart of the tile= and swz= arguments of h3metal/ops.py:124-126. Returns 0. */
-H3B_API int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band);
+/* Overrides the product's choices: tile_n (0 = automatic; 32, 64, 128, 256: single-CTA tiles of that width), band
+ * (row tiles swept per column tile, 0 = automatic) and pair (CTA pairs computing 256 x 256 tiles with
+ * tcgen05.mma cta_group::2: 1 = whenever no low-rank term is attached; 0 or -1 = never, the default). The
+ * counterpart of the tile= and swz= arguments of h3metal/ops.py:124-126. Returns 0. */
+H3B_API int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band, int pair);
 /* Tuning of the rotate+quantise kernel. tma_stages: rows a CTA keeps in flight in shared memory (1..4), 0 =
  * automatic, -1 = do not use the TMA-fed kernel. threads_target: CTA size target of the register-fed kernel that
  * serves fp32 inputs, rows over 16384 channels and tma_stages = -1 (0 = automatic). The counterpart of the NSG/MAXB

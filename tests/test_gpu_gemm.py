@@ -24,23 +24,34 @@ def _case(rng, M, N, K, full_range=True):
     return m_pad, a, w, sa, sw
 
 
-def _gemm(gpu, a, w, sa, sw, M, out_dtype, bias=None, tile=(64, 32, 2), **kw):
+PAIR = {"single": -1, "pair": 1}  # the product on single CTAs (128-row tiles) or on CTA pairs (256 x 256 tiles)
+
+
+def _gemm(gpu, a, w, sa, sw, M, out_dtype, bias=None, tile=(64, 32, 2), variant=None, **kw):
     N, K = w.shape
     wt = ops.QWeight("q8", gpu.upload(w), gpu.upload(sw), N, K, bias=gpu.upload(bias) if bias is not None else None)
     out = gpu.empty((a.shape[0], N), out_dtype)
-    ops.gemm(gpu, gpu.upload(a), wt, out, M, sa=gpu.upload(sa), tile=tile, **kw)
-    gpu.wait()
+    if variant is not None:
+        gpu.set_policy(pair=PAIR[variant])
+    try:
+        ops.gemm(gpu, gpu.upload(a), wt, out, M, sa=gpu.upload(sa), tile=tile, **kw)
+        gpu.wait()
+    finally:
+        if variant is not None:
+            gpu.set_policy()
     return out.numpy()
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 32, 64), (128, 32, 128), (128, 64, 256), (128, 256, 512), (127, 128, 128),
                                    (129, 256, 640), (200, 256, 512), (256, 512, 1024), (384, 768, 3072),
-                                   (1000, 1152, 640), (130, 96, 192), (64, 3872, 256), (300, 160, 16384)])
-def test_accumulators_bit_exact(gpu, M, N, K):
+                                   (1000, 1152, 640), (130, 96, 192), (64, 3872, 256), (300, 160, 16384),
+                                   (2304, 2560, 1152), (2100, 1056, 384)])
+@pytest.mark.parametrize("variant", ["single", "pair"])
+def test_accumulators_bit_exact(gpu, variant, M, N, K):
     rng = np.random.default_rng(M + 7 * N + 13 * K)
     m_pad, a, w, sa, sw = _case(rng, M, N, K)
     rows = (M + 63) // 64 * 64  # the rows a (64, ., .) tile writes
-    got = _gemm(gpu, a, w, sa, sw, M, "i32")
+    got = _gemm(gpu, a, w, sa, sw, M, "i32", variant=variant)
     assert np.array_equal(got[:rows], gemm_ref.int32_product(a[:rows], w))
     assert not got[rows:].any()  # rows beyond the padded count are not touched
 
@@ -53,10 +64,11 @@ def test_accumulators_at_int32_extremes(gpu):
     w = np.full((32, K), 127, np.int8)
     w[::3] = -127
     ones_m, ones_n = np.ones(128, np.float32), np.ones(32, np.float32)
-    acc = _gemm(gpu, a, w, ones_m, ones_n, 128, "i32")
-    assert np.array_equal(acc, gemm_ref.int32_product(a, w)) and abs(int(acc[0, 1])) == K * 127 * 127
-    v = _gemm(gpu, a, w, ones_m, ones_n, 128, "f32")
-    assert np.array_equal(v, gemm_ref.epilogue_q8(gemm_ref.int32_product(a, w), ones_m, ones_n))
+    for variant in ("single", "pair"):
+        acc = _gemm(gpu, a, w, ones_m, ones_n, 128, "i32", variant=variant)
+        assert np.array_equal(acc, gemm_ref.int32_product(a, w)) and abs(int(acc[0, 1])) == K * 127 * 127
+        v = _gemm(gpu, a, w, ones_m, ones_n, 128, "f32", variant=variant)
+        assert np.array_equal(v, gemm_ref.epilogue_q8(gemm_ref.int32_product(a, w), ones_m, ones_n))
 
 
 @pytest.mark.parametrize("tile_n", [32, 64, 128, 256])
@@ -71,11 +83,12 @@ def test_every_tile_width_is_exact(gpu, tile_n):
     assert np.array_equal(got, gemm_ref.int32_product(a, w))
 
 
+@pytest.mark.parametrize("pair", [-1, 1])
 @pytest.mark.parametrize("band", [1, 2, 5])
-def test_tile_order_does_not_change_results(gpu, band):
+def test_tile_order_does_not_change_results(gpu, band, pair):
     rng = np.random.default_rng(band)
     m_pad, a, w, sa, sw = _case(rng, 1280, 1536, 512)
-    gpu.set_policy(0, band)
+    gpu.set_policy(0, band, pair=pair)
     try:
         got = _gemm(gpu, a, w, sa, sw, 1280, "i32")
     finally:
@@ -83,14 +96,15 @@ def test_tile_order_does_not_change_results(gpu, band):
     assert np.array_equal(got, gemm_ref.int32_product(a, w))
 
 
+@pytest.mark.parametrize("variant", ["single", "pair"])
 @pytest.mark.parametrize("out_dtype", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("with_bias", [False, True])
-def test_epilogue_matches_oracle_bit_for_bit(gpu, out_dtype, with_bias):
+def test_epilogue_matches_oracle_bit_for_bit(gpu, out_dtype, with_bias, variant):
     rng = np.random.default_rng(17)
     M, N, K = 200, 256, 512
     m_pad, a, w, sa, sw = _case(rng, M, N, K)
     bias = (rng.standard_normal(N) * 0.01).astype(np.float32) if with_bias else None
-    got = _gemm(gpu, a, w, sa, sw, M, out_dtype, bias=bias, tile=(64, 128, 4))
+    got = _gemm(gpu, a, w, sa, sw, M, out_dtype, bias=bias, tile=(64, 128, 4), variant=variant)
     stored, v, _ = gemm_ref.gemm_q8(a, w, sa, sw, bias, None, out_dtype)
     assert np.array_equal(got, stored)
     # acceptance bound on dequantised outputs, like with like
