@@ -109,8 +109,10 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
   for (int m = blockIdx.x; m < p.M; m += gridDim.x, ++it) {
     const int s = it % p.stages;
     const uint32_t ph = (it / p.stages) & 1u;
-    const bool arrived = mbar_wait(bars + 8u * s, ph, cta_abort, p.status, kStatusRotTimeout);
-    if (!__syncthreads_and(arrived)) break;  // uniform decision: either every thread goes on or none does
+    // One thread polls the stage's barrier (a whole CTA spinning on it would eat the issue slots the arithmetic
+    // needs); the CTA barrier then releases everybody with a uniform decision: all threads go on or none does.
+    const bool arrived = tid != 0 || mbar_wait(bars + 8u * s, ph, cta_abort, p.status, kStatusRotTimeout);
+    if (!__syncthreads_and(arrived)) break;
 
     const uint8_t *stage = base_ptr + s * p.stage_bytes;
     float v[kChunk];
@@ -252,7 +254,9 @@ void rot_q8_tma_plan(int D, int mode, int stages_wanted, int *threads, int *stag
   const int row = (D * 2 + 1023) / 1024 * 1024;
   *gate_offset = row;
   *stage_bytes = mode == 1 ? 2 * row : row;
-  int s = stages_wanted > 0 ? stages_wanted : 2;  // one row ahead measured best at every size tried
+  // measured: one row ahead (2 stages) is best for plain rows; with gates a stage is twice as large and a single
+  // stage, which lets more CTAs share an SM, wins
+  int s = stages_wanted > 0 ? stages_wanted : (mode == 1 ? 1 : 2);
   if (s > kMaxStages) s = kMaxStages;
   while (s > 1 && static_cast<size_t>(s) * *stage_bytes + 2048 > 232448) --s;
   *stages = s;
