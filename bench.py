@@ -49,7 +49,10 @@ def measured_peaks():
 
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu capture
 # summarised under profiles/), keyed by workload; None until a capture exists for it.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # profiles/gemm_w8a8_config1_ncu.md: 536.6 MB over the step's four product launches
+    "config 1": 134.1e6,
+}
 
 
 class ClockSampler:
@@ -273,7 +276,9 @@ def run_ours(args, cfg, rank, world):
     wl = workload_name(cfg)
     roofline = {"bound": "tensor", "kernel": "gemm_w8a8_kernel (tcgen05 kind::i8)", "achieved": achieved_tops,
                 "peak": peaks["int8_tops"], "unit": "TOP/s", "frac": achieved_tops / peaks["int8_tops"],
-                "traffic": NCU_TRAFFIC_BYTES.get(wl), "peak_source": peaks["source"],
+                "traffic": NCU_TRAFFIC_BYTES.get(wl.split(":")[0]),
+                "algorithmic_bytes": sum(l.m_pad * l.wt.K + l.wt.N * l.wt.K + 2 * l.m_pad * l.wt.N for l in blk.layers) / len(blk.layers),
+                "peak_source": peaks["source"],
                 "frac_of_nominal_4500": achieved_tops / NOMINAL_INT8_TOPS,
                 "time_share": gemm_s / (gemm_s + rot_s)}
     roofline_rot = {"bound": "hbm", "kernel": "rot_q8_kernel", "achieved": rot_gbs, "peak": peaks["hbm_gbs"],
@@ -281,28 +286,37 @@ def run_ours(args, cfg, rank, world):
                     "time_share": rot_s / (gemm_s + rot_s)}
 
     # ---- end to end through the public API with HOST buffers: H2D of every input, D2H of every output ---------------
-    host_in, host_out = [], []
-    for layer, x in zip(blk.layers, blk.inputs):
-        if x is not None:
-            host_in.append((torch.empty(x.shape, dtype=torch.bfloat16).pin_memory().copy_(x.torch().cpu()), x.torch()))
-    for i, layer in enumerate(blk.layers):
-        consumed = i + 1 < len(blk.layers) and blk.inputs[i + 1] is None  # feeds the next linear on the device
-        if not consumed:
-            host_out.append((torch.empty(layer.out.shape, dtype=torch.bfloat16).pin_memory(), layer.out.torch()))
-    h2d = sum(h.numel() * 2 for h, _ in host_in)
-    d2h = sum(h.numel() * 2 for h, _ in host_out)
+    host_in, host_out = blk.host_buffers()
+    for h, x in zip(host_in, blk.inputs):
+        if h is not None:
+            h.copy_(x.torch().cpu())
+    h2d = sum(h.numel() * 2 for h in host_in if h is not None)
+    d2h = sum(h.numel() * 2 for h in host_out if h is not None)
 
     def e2e_step():
-        with torch.cuda.stream(gpu.stream):
-            for h, d in host_in:
-                d.copy_(h, non_blocking=True)
-            blk.step()
-            for h, d in host_out:
-                h.copy_(d, non_blocking=True)
+        blk.step_host(host_in, host_out)
+
+    def timed_e2e(steps):
+        """Like timed(), but the region ends when the LAST download has landed in host memory."""
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        blk.sync_host()
+        barrier()
+        start.record(gpu.stream)
+        for _ in range(steps):
+            e2e_step()
+        blk._down.wait_stream(blk._up)
+        gpu.stream.wait_stream(blk._down)
+        end.record(gpu.stream)
+        blk.sync_host()
+        ms = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
+        barrier()
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
 
     for _ in range(2):
         e2e_step()
-    e2e_ms = timed(e2e_step, args.steps)
+    e2e_ms = timed_e2e(args.steps)
     e2e_value = tokens / (e2e_ms * 1e-3)
 
     if world > 1:
