@@ -286,38 +286,42 @@ def run_ours(args, cfg, rank, world):
                     "time_share": rot_s / (gemm_s + rot_s)}
 
     # ---- end to end through the public API with HOST buffers: H2D of every input, D2H of every output ---------------
-    host_in, host_out = blk.host_buffers()
-    for h, x in zip(host_in, blk.inputs):
-        if h is not None:
-            h.copy_(x.torch().cpu())
-    h2d = sum(h.numel() * 2 for h in host_in if h is not None)
-    d2h = sum(h.numel() * 2 for h in host_out if h is not None)
+    e2e = None
+    if not args.no_e2e:
+        host_in, host_out = blk.host_buffers()
+        for h, x in zip(host_in, blk.inputs):
+            if h is not None:
+                h.copy_(x.torch().cpu())
+        h2d = sum(h.numel() * 2 for h in host_in if h is not None)
+        d2h = sum(h.numel() * 2 for h in host_out if h is not None)
 
-    def e2e_step():
-        blk.step_host(host_in, host_out)
+        def e2e_step():
+            blk.step_host(host_in, host_out)
 
-    def timed_e2e(steps):
-        """Like timed(), but the region ends when the LAST download has landed in host memory."""
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        blk.sync_host()
-        barrier()
-        start.record(gpu.stream)
-        for _ in range(steps):
+        def timed_e2e(steps):
+            """Like timed(), but the region ends when the LAST download has landed in host memory."""
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            blk.sync_host()
+            barrier()
+            start.record(gpu.stream)
+            for _ in range(steps):
+                e2e_step()
+            blk._down.wait_stream(blk._up)
+            gpu.stream.wait_stream(blk._down)
+            end.record(gpu.stream)
+            blk.sync_host()
+            ms = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
+            barrier()
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            return float(ms.item())
+
+        for _ in range(2):
             e2e_step()
-        blk._down.wait_stream(blk._up)
-        gpu.stream.wait_stream(blk._down)
-        end.record(gpu.stream)
-        blk.sync_host()
-        ms = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
-        barrier()
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    for _ in range(2):
-        e2e_step()
-    e2e_ms = timed_e2e(args.steps)
-    e2e_value = tokens / (e2e_ms * 1e-3)
+        e2e_ms = timed_e2e(args.steps)
+        e2e_value = tokens / (e2e_ms * 1e-3)
+        e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_ms / args.steps}
 
     if world > 1:
         dist.barrier()
@@ -328,11 +332,12 @@ def run_ours(args, cfg, rank, world):
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
         "config": {"workload": wl, "block": cfg.block, "parallelism": f"token-sharded x{world} (no collective)",
-                   "l2": "per-step working set (int8 weights 177 MB + activations and outputs 0.5 GB) exceeds the 126 MB L2"},
+                   "l2": f"per-step working set ({sum(l.wt.N * l.wt.K for l in blk.layers) / 1e6:.0f} MB of int8 weights plus "
+                         f"{sum(2 * l.m_pad * (l.wt.K + l.wt.N) for l in blk.layers) / 1e9:.2f} GB of activations and outputs) "
+                         f"exceeds the 126 MB L2"},
         "tops": value / cfg.M * cfg.ops / 1e12 ,
         "roofline": roofline, "roofline_rot_q8": roofline_rot,
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms / args.steps},
+        "e2e": e2e,
         "gpu_launches": int(launches),
         "clocks": dict(clocks.summary(), window=f"timed region + {extra_steps} identical steps run straight after it"),
     }
@@ -383,6 +388,34 @@ def run_tensor_parallel(args, cfg, rank, world, gpu):
             "tops": value / cfg.M * cfg.ops / 1e12, "gpu_launches": None}
 
 
+def library_int8_probe():
+    """Yardstick, not part of the path: what the vendor library's int8 GEMM (cuBLASLt through torch._int_mm, int32
+    output, no epilogue) and its bf16 GEMM reach on this GPU under the same power cap, for cubes of three sizes.
+    Prints one JSON line."""
+    import torch
+    out = {"probe": "library int8 / bf16 GEMM", "results": []}
+    for n in (4096, 8192, 16384):
+        a = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
+        b = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8).t()
+        x = torch.randn(n, n, device="cuda", dtype=torch.bfloat16)
+        y = torch.randn(n, n, device="cuda", dtype=torch.bfloat16)
+        reps = 20 if n < 16384 else 8
+        row = {"n": n}
+        for name, fn in (("int8_tops", lambda: torch._int_mm(a, b)), ("bf16_tflops", lambda: x @ y)):
+            for _ in range(3):
+                fn()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(reps):
+                fn()
+            end.record()
+            torch.cuda.synchronize()
+            row[name] = 2 * n ** 3 / (start.elapsed_time(end) / reps * 1e-3) / 1e12
+        out["results"].append(row)
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -392,12 +425,18 @@ def main():
     ap.add_argument("--config", type=int, default=1)
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (0 = default)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (it pins GBs of host memory on the largest configs)")
     ap.add_argument("--parallel", default="token", choices=["token", "tp"],
                     help="N > 1: token = every rank its own M tokens (default, weak scaling); tp = ONE block of M tokens "
                          "sharded column-/row-parallel over the ranks with NCCL all-reduces (strong scaling)")
     ap.add_argument("--reduce", default="int32", choices=["int32", "f32", "bf16"],
                     help="tp: what the row-parallel layers all-reduce (int32 = bit-exact)")
+    ap.add_argument("--library-int8-probe", action="store_true",
+                    help="time the vendor library's int8 and bf16 GEMMs on this GPU (a yardstick; runs nothing of the path)")
     args = ap.parse_args()
+    if args.library_int8_probe:
+        library_int8_probe()
+        return
 
     from h3metal_b200 import workloads
     cfg = workloads.CONFIGS[args.config]
