@@ -149,7 +149,19 @@ class CpuBlock:
         return prev
 
 
+def use_all_host_threads() -> int:
+    """BLAS on every host core (a launcher such as torch.distributed.run pins OMP_NUM_THREADS to 1)."""
+    n = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=n)
+    except Exception:
+        pass
+    return n
+
+
 def time_cpu(cfg, rows: int, steps: int, warmup: int):
+    use_all_host_threads()
     blk = CpuBlock(cfg, rows)
     for _ in range(warmup):
         blk.step()
@@ -361,7 +373,7 @@ def run_tensor_parallel(args, cfg, rank, world, gpu):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29531")
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=gpu.torch_device)
-    blk = TensorParallelBlock(gpu, None, cfg, seed=99, reduce=args.reduce)
+    blk = TensorParallelBlock(gpu, None, cfg, seed=99, reduce=args.reduce, scatter=args.scatter)
     dev = gpu.torch_device
     for _ in range(max(args.warmup, 3)):
         blk.step()
@@ -384,7 +396,7 @@ def run_tensor_parallel(args, cfg, rank, world, gpu):
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": workload_name(cfg), "block": cfg.block,
-                       "parallelism": f"tp{world}: column-parallel qkv/w1w3, row-parallel out/w2 ({args.reduce} all-reduce)"},
+                       "parallelism": f"tp{world}: column-parallel qkv/w1w3, row-parallel out/w2 ({args.reduce} {'reduce-scatter' if args.scatter else 'all-reduce'})"},
             "tops": value / cfg.M * cfg.ops / 1e12, "gpu_launches": None}
 
 
@@ -431,6 +443,8 @@ def main():
                          "sharded column-/row-parallel over the ranks with NCCL all-reduces (strong scaling)")
     ap.add_argument("--reduce", default="int32", choices=["int32", "f32", "bf16"],
                     help="tp: what the row-parallel layers all-reduce (int32 = bit-exact)")
+    ap.add_argument("--scatter", action="store_true",
+                    help="tp: reduce-scatter instead of all-reduce (every rank finishes its M / N_gpus rows)")
     ap.add_argument("--library-int8-probe", action="store_true",
                     help="time the vendor library's int8 and bf16 GEMMs on this GPU (a yardstick; runs nothing of the path)")
     args = ap.parse_args()

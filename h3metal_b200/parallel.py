@@ -14,8 +14,10 @@ row-parallel    W's columns (K) are split; the input arrives already sharded on 
                 (kernels/ops.metal:315-317), so: (1) every rank rotates its shard and reports the row maxima,
                 (2) MAX all-reduce of M floats, (3) every rank quantises with the reduced maximum, (4) int8 product
                 into raw int32 accumulators, (5) SUM all-reduce of the int32 partials - integer addition is exact in
-                any order - (6) one epilogue (h3b_dequant_i32). Result: bit-identical to one GPU at any p. A faster,
-                approximate variant reduces dequantised fp32 or bf16 partials instead (`reduce="f32" | "bf16"`).
+                any order - (6) one epilogue (h3b_dequant_i32). Result: bit-identical to one GPU at any p. With
+                `scatter=True` step (5) is a reduce-scatter and every rank finishes only its M / p rows (what a
+                following per-token operation needs; half the traffic). A faster, approximate variant all-reduces
+                dequantised fp32 or bf16 partials instead (`reduce="f32" | "bf16"`).
                 K / p must be a multiple of the rotation block. A LoRA term on a row-parallel layer is not supported.
 
 Collectives run on torch's current stream, which is also the stream the kernels are launched on, so a layer is
@@ -125,11 +127,13 @@ class RowParallelLinear:
     swiglu_in). The output [M][N] is complete on every rank after the reduction."""
 
     def __init__(self, gpu: Gpu, group, codes, scales, bias, M: int, *, block: int = 128, swiglu_in: bool = False,
-                 out_dtype: str = "bf16", reduce: str = "int32"):
+                 out_dtype: str = "bf16", reduce: str = "int32", scatter: bool = False):
         dist = _dist()
         if reduce not in ("int32", "f32", "bf16"):
             raise ValueError(f"reduce={reduce!r}")
-        self.group, self.reduce = group, reduce
+        if scatter and reduce != "int32":
+            raise ValueError("scatter=True is implemented for the exact (int32) reduction")
+        self.group, self.reduce, self.scatter = group, reduce, scatter
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         N, K = codes.shape
         k0, k1 = shard_bounds(int(K), self.rank, self.world, block)
@@ -143,7 +147,11 @@ class RowParallelLinear:
         self.sa = gpu.empty((self.m_pad,), "f32")
         self.out = gpu.empty((self.m_pad, int(N)), out_dtype)
         self.partial = gpu.empty((self.m_pad, int(N)), {"int32": "i32", "f32": "f32", "bf16": "bf16"}[reduce])
-        self._ones = None
+        if scatter:  # every rank keeps only its M / p rows of the result: half the traffic of an all-reduce
+            self.r0, r1 = shard_bounds(self.m_pad, self.rank, self.world, 1)
+            self.rows = r1 - self.r0
+            self.part_rows = gpu.empty((self.rows, int(N)), "i32")
+            self.out = gpu.empty((self.rows, int(N)), out_dtype)
 
     def __call__(self, x_local: Tensor, x_stride: int | None = None) -> Tensor:
         dist = _dist()
@@ -159,6 +167,16 @@ class RowParallelLinear:
         # (4)-(6)
         if self.reduce == "int32":
             ops.gemm(gpu, self.a8, wt, self.partial, M, sa=self.sa, tile=(128, 32, 4))  # i32 output: raw accumulators
+            if self.scatter:
+                if self.world > 1:
+                    dist.reduce_scatter_tensor(self.part_rows.torch(), self.partial.torch(), op=dist.ReduceOp.SUM,
+                                               group=self.group)
+                    acc = self.part_rows
+                else:
+                    acc = self.partial
+                gpu.dequant_native(acc, wt.N, self.sa.view((self.rows,), offset_elems=self.r0), wt.sw, self.bias, self.out,
+                                   wt.N, self.rows, wt.N)
+                return self.out  # rows [r0, r0 + rows) of the layer's output
             if self.world > 1:
                 dist.all_reduce(self.partial.torch(), op=dist.ReduceOp.SUM, group=self.group)
             gpu.dequant_native(self.partial, wt.N, self.sa, wt.sw, self.bias, self.out, wt.N, self.m_pad, wt.N)
@@ -179,7 +197,7 @@ class TensorParallelBlock:
     synthetic weights drawn per rank on the device (timing only). Inputs that the model's attention and norm kernels
     would produce (outside this path) are synthetic buffers of the right, sharded shapes."""
 
-    def __init__(self, gpu: Gpu, group, cfg, seed: int = 0, reduce: str = "int32"):
+    def __init__(self, gpu: Gpu, group, cfg, seed: int = 0, reduce: str = "int32", scatter: bool = False):
         import torch
         from . import workloads
         dist = _dist()
@@ -206,7 +224,7 @@ class TensorParallelBlock:
             else:
                 codes, scales = workloads.weight_torch(gen, spec.N, spec.K, dev)
                 layer = RowParallelLinear(gpu, group, codes, scales, bias, M, block=cfg.block,
-                                          swiglu_in=spec.swiglu_in, reduce=reduce)
+                                          swiglu_in=spec.swiglu_in, reduce=reduce, scatter=scatter)
                 if spec.swiglu_in:
                     self.inputs.append(None)  # the previous (column-parallel) layer's local value | gate output
                 else:

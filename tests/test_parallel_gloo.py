@@ -64,13 +64,15 @@ def _worker(rank, port, results):
         down = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True)
         h_local = up(g.upload(x, "bf16"))
         y = down(h_local)
+        down_rs = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True, scatter=True)
+        y_rows = down_rs(h_local)
         down_f32 = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True, reduce="f32")
         y_fast = down_f32(h_local)
         tok = parallel.TokenShardedLinear(g, None, parallel.ops.QWeight("q8", g.upload(w_up), g.upload(s_up), 2 * F, D,
                                                                          bias=g.upload(b_up)), M, block=BLOCK)
         h_tok = tok(g.upload(x[tok.m0:tok.m0 + tok.rows], "bf16"))
         results[rank] = dict(slices=up.slices, h_local=h_local.numpy().copy(), a8=down.a8.numpy().copy(),
-                             sa=down.sa.numpy().copy(), y=y.numpy().copy(), y_fast=y_fast.numpy().copy(),
+                             sa=down.sa.numpy().copy(), y=y.numpy().copy(), y_rows=(down_rs.r0, y_rows.numpy().copy()), y_fast=y_fast.numpy().copy(),
                              tok=(tok.m0, tok.rows, h_tok.numpy().copy()))
     finally:
         dist.destroy_process_group()
@@ -94,6 +96,8 @@ def test_two_ranks_reproduce_one_rank_bit_for_bit():
         assert np.array_equal(r["a8"], q2[:, rank * half:(rank + 1) * half])
         assert np.array_equal(r["sa"], s2)
         assert np.array_equal(r["y"], y)
+        r0, y_rows = r["y_rows"]  # reduce-scatter: this rank's rows of the same exact result
+        assert r0 == rank * M // WORLD and np.array_equal(y_rows, y[r0:r0 + M // WORLD])
         # approximate variant (fp32 partials): inside the path's 1e-3 bound
         got = oracle.bf16_bits_to_f32(r["y_fast"]).astype(np.float64)
         want = oracle.bf16_bits_to_f32(y).astype(np.float64)
