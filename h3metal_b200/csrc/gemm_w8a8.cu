@@ -33,9 +33,10 @@ namespace {
 
 using namespace gemm;
 
-template <int BN, int ACC_STAGES, bool LORA>
-__global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_constant__ GemmLaunch g,
-                                                                const int stages) {
+template <int BN, int ACC_STAGES, bool LORA, int EPI_WARPS>
+__global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const __grid_constant__ GemmLaunch g,
+                                                                           const int stages) {
+  static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "one or two epilogue warps per TMEM lane quarter");
   static_assert(ACC_STAGES * BN <= (LORA ? kLowBase : kTmemCols), "accumulators do not fit tensor memory");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -57,7 +58,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_con
   const uint32_t lora_full_bar = bars + 160u, lora_empty_bar = bars + 168u;
   volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(base_ptr + bars_off + 176);
   volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + bars_off + 180);
-  float *col_stage = reinterpret_cast<float *>(base_ptr + bars_off + kBarrierBytes);  // [4 warps][2][BN]: sw, bias
+  float *col_stage = reinterpret_cast<float *>(base_ptr + bars_off + kBarrierBytes);  // [EPI_WARPS][2][BN]: sw, bias
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (g.M + kBM - 1) / kBM, n_tiles = (g.N + BN - 1) / BN;
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_con
     }
     for (int i = 0; i < ACC_STAGES; ++i) {
       mbar_init(acc_full_bar(i), 1);
-      mbar_init(acc_empty_bar(i), 4);  // one arrival per epilogue warp
+      mbar_init(acc_empty_bar(i), EPI_WARPS);  // one arrival per epilogue warp
     }
     mbar_init(lora_full_bar, 1);
     mbar_init(lora_empty_bar, 1);
@@ -191,8 +192,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_con
       }
     }
   } else {
-    // ---------------------------------------------------------------------------------- epilogue (warps 2..5)
-    const int quarter = warp & 3;  // TMEM lanes 32 * quarter .. + 31 are the ones this warp may read
+    // ---------------------------------------------------------------------------------- epilogue (warps 2 ..)
+    // A warp may only read the TMEM lanes of its quarter (warp index mod 4). With eight epilogue warps two warps
+    // share a quarter and split the tile's columns between them.
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;                          // 0, or 1 for the second warp of a quarter
+    constexpr int kChunks = BN / 32;
+    constexpr int kPerWarp = EPI_WARPS == 8 && kChunks >= 2 ? kChunks / 2 : kChunks;
+    const int c_begin = EPI_WARPS == 8 && kChunks >= 2 ? half * kPerWarp : 0;
+    const int c_end = (EPI_WARPS == 8 && kChunks < 2 && half == 1) ? c_begin : c_begin + kPerWarp;
     const int row = quarter * 32 + lane;
     const bool raw = g.c_dtype == kDtypeI32;
     const size_t esize = (g.c_dtype == kDtypeF32 || raw) ? 4 : 2;
@@ -205,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_con
       const int as = at % ACC_STAGES;
       const uint32_t aph = (at / ACC_STAGES) & 1u;
       // per-column scale and bias of this tile -> this warp's own slice of shared memory (no cross-warp barrier)
-      float *sw_s = col_stage + quarter * 2 * BN, *bias_s = sw_s + BN;
+      float *sw_s = col_stage + (warp - 2) * 2 * BN, *bias_s = sw_s + BN;
       stage_columns(g, n0, BN, lane, sw_s, bias_s);
       const int m = m0 + row;
       const float sa_m = (!raw && m < g.M) ? __ldg(g.sa + m) : 0.0f;
@@ -223,14 +231,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_con
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN;
       const uint32_t t_low = t_acc + kLowBase;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t acc[32];
-        uint32_t low[32];
+      // two register sets: the TMEM loads of the next 32 columns are in flight while this chunk is finished
+      uint32_t acc_a[32], low_a[32], acc_b[32], low_b[32];
+      auto fetch = [&](int c, uint32_t (&acc)[32], uint32_t (&low)[32]) {
         tmem_ld_32x32b_x32(t_acc + c * 32, acc);
         if (LORA && has_low) tmem_ld_32x32b_x32(t_low + c * 32, low);
+      };
+      if (c_begin < c_end) fetch(c_begin, acc_a, low_a);
+#pragma unroll 1
+      for (int c = c_begin; c < c_end; c += 2) {
         tmem_ld_wait();
-        finish_chunk(g, acc, low, LORA && has_low, m, n0 + c * 32, sa_m, sw_s + c * 32, bias_s + c * 32, vec_ok);
+        if (c + 1 < c_end) fetch(c + 1, acc_b, low_b);
+        finish_chunk(g, acc_a, low_a, LORA && has_low, m, n0 + c * 32, sa_m, sw_s + c * 32, bias_s + c * 32, vec_ok);
+        if (c + 1 < c_end) {
+          tmem_ld_wait();
+          if (c + 2 < c_end) fetch(c + 2, acc_a, low_a);
+          finish_chunk(g, acc_b, low_b, LORA && has_low, m, n0 + (c + 1) * 32, sa_m, sw_s + (c + 1) * 32,
+                       bias_s + (c + 1) * 32, vec_ok);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -247,16 +265,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w8a8_kernel(const __grid_con
   }
 }
 
-template <int BN, int ACC_STAGES, bool LORA>
+template <int BN, int ACC_STAGES, bool LORA, int EPI>
 cudaError_t launch_one(const GemmLaunch &g, int stages, cudaStream_t stream) {
   const size_t smem = gemm_smem_bytes(BN, LORA ? g.R : 0, stages);
-  gemm_w8a8_kernel<BN, ACC_STAGES, LORA><<<g.grid, kThreads, smem, stream>>>(g, stages);
+  gemm_w8a8_kernel<BN, ACC_STAGES, LORA, EPI><<<g.grid, 64 + 32 * EPI, smem, stream>>>(g, stages);
   return cudaGetLastError();
 }
 
-template <int BN, int ACC_STAGES, bool LORA>
+template <int BN, int ACC_STAGES, bool LORA, int EPI>
 cudaError_t configure_one() {
-  return cudaFuncSetAttribute(gemm_w8a8_kernel<BN, ACC_STAGES, LORA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  return cudaFuncSetAttribute(gemm_w8a8_kernel<BN, ACC_STAGES, LORA, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               232448);
 }
 
@@ -266,7 +284,7 @@ size_t gemm_smem_bytes(int bn, int R, int stages) {
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return 0;
   if (R % kLoraChunk) return 0;
   return 1024 + static_cast<size_t>(stages) * stage_bytes(bn) + lora_bytes(bn, R) + kBarrierBytes +
-         8 * static_cast<size_t>(bn) * sizeof(float);
+         16 * static_cast<size_t>(bn) * sizeof(float);  // column staging for up to eight epilogue warps
 }
 
 int gemm_pick_stages(int bn, int R, size_t smem_optin) {
@@ -279,10 +297,10 @@ int gemm_pick_stages(int bn, int R, size_t smem_optin) {
 
 cudaError_t gemm_configure(int /*device*/) {
   cudaError_t e;
-#define H3B_CFG(BN, AS, L) \
-  if ((e = configure_one<BN, AS, L>()) != cudaSuccess) return e;
-  H3B_CFG(32, 2, false) H3B_CFG(64, 2, false) H3B_CFG(128, 2, false) H3B_CFG(256, 2, false)
-  H3B_CFG(32, 2, true) H3B_CFG(64, 2, true) H3B_CFG(128, 2, true) H3B_CFG(256, 1, true)
+#define H3B_CFG(BN, AS, L, E) \
+  if ((e = configure_one<BN, AS, L, E>()) != cudaSuccess) return e;
+  H3B_CFG(32, 2, false, 4) H3B_CFG(64, 2, false, 4) H3B_CFG(128, 2, false, 4) H3B_CFG(256, 2, false, 4)
+  H3B_CFG(32, 2, true, 4) H3B_CFG(64, 2, true, 4) H3B_CFG(128, 2, true, 4) H3B_CFG(256, 1, true, 4)
 #undef H3B_CFG
   return cudaSuccess;
 }
@@ -290,10 +308,14 @@ cudaError_t gemm_configure(int /*device*/) {
 cudaError_t launch_gemm_w8a8(const GemmLaunch &g, int stages, cudaStream_t stream) {
   const bool lora = g.R > 0;
   switch (g.bn) {
-    case 32: return lora ? launch_one<32, 2, true>(g, stages, stream) : launch_one<32, 2, false>(g, stages, stream);
-    case 64: return lora ? launch_one<64, 2, true>(g, stages, stream) : launch_one<64, 2, false>(g, stages, stream);
-    case 128: return lora ? launch_one<128, 2, true>(g, stages, stream) : launch_one<128, 2, false>(g, stages, stream);
-    case 256: return lora ? launch_one<256, 1, true>(g, stages, stream) : launch_one<256, 2, false>(g, stages, stream);
+    case 32: return lora ? launch_one<32, 2, true, 4>(g, stages, stream) : launch_one<32, 2, false, 4>(g, stages, stream);
+    case 64: return lora ? launch_one<64, 2, true, 4>(g, stages, stream) : launch_one<64, 2, false, 4>(g, stages, stream);
+    case 128: return lora ? launch_one<128, 2, true, 4>(g, stages, stream) : launch_one<128, 2, false, 4>(g, stages, stream);
+    case 256:
+      // A low-rank term on 256-column tiles leaves room for ONE accumulator pair in tensor memory, so its epilogue
+      // (about 3 us per tile) does not overlap the next tile's main loop. Measured alternatives were slower: a
+      // second epilogue warp per lane quarter (-15 %) and 128-column tiles with two accumulator pairs (-25 %).
+      return lora ? launch_one<256, 1, true, 4>(g, stages, stream) : launch_one<256, 2, false, 4>(g, stages, stream);
     default: return cudaErrorInvalidValue;
   }
 }
