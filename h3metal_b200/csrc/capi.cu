@@ -327,6 +327,31 @@ int h3b_rot_q8_given_amax(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_st
   return rot_enqueue(ctx, x, x_dtype, x_stride, out, amax_to_scale, M, D, block, mode, 0, 2);
 }
 
+int h3b_norm_mod_q8(h3b_ctx *ctx, float *x, int64_t x_stride, const float *mod, int64_t mod_stride,
+                    const uint8_t *rtype, void *out, float *sa, int M, int D, int block, float eps, int ln, int out_kind,
+                    const float *y, const float *post) {
+  if (!ctx) return fail("null context");
+  if (!x || !mod || !rtype || !out) return fail("norm_mod_q8: null tensor argument");
+  if (out_kind < 0 || out_kind > 3) return fail("norm_mod_q8: out_kind must be 0 (int8), 1 (fp32), 2 (fp16) or 3 (rotated fp16)");
+  if (out_kind == 0 && !sa) return fail("norm_mod_q8: int8 output needs the row-scale buffer");
+  if (M <= 0 || D <= 0) return fail("norm_mod_q8: M and D must be positive");
+  if (block != 64 && block != 128 && block != 256) return fail("norm_mod_q8: rotation block must be 64, 128 or 256");
+  if (D % block) return fail("norm_mod_q8: D " + std::to_string(D) + " is not a multiple of the rotation block " + std::to_string(block));
+  if ((post != nullptr) != (y != nullptr)) return fail("norm_mod_q8: y and post go together");
+  if (ln && post) return fail("norm_mod_q8: LayerNorm excludes the fused residual update");
+  if (x_stride < D || mod_stride < 2LL * D) return fail("norm_mod_q8: x_stride / mod_stride smaller than the row");
+  if (D > (post ? 16384 : 32768)) return fail("norm_mod_q8: D exceeds what one CTA covers (32768; 16384 with the residual update)");
+  if (reinterpret_cast<uintptr_t>(x) % 16 || (x_stride * 4) % 16 || reinterpret_cast<uintptr_t>(mod) % 16 ||
+      (mod_stride * 4) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
+      (y && reinterpret_cast<uintptr_t>(y) % 16) || (post && reinterpret_cast<uintptr_t>(post) % 16))
+    return fail("norm_mod_q8: tensors must be 16-byte aligned with row strides that are multiples of 16 bytes");
+  cudaEvent_t ps = nullptr;
+  if (ctx->before_launch(&ps)) return -1;
+  const cudaError_t e = h3b::launch_norm_mod_q8(x, x_stride, mod, mod_stride, rtype, out, sa, M, D, block, eps, ln, out_kind,
+                                                y, post, ctx->stream);
+  return ctx->after_launch("norm_mod_q8 launch", e);
+}
+
 int h3b_dequant_i32(h3b_ctx *ctx, const int32_t *acc, int64_t acc_stride, const float *sa, const float *sw,
                     const float *bias, void *C, int c_dtype, int64_t c_stride, int M, int N) {
   if (!ctx) return fail("null context");

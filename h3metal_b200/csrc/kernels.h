@@ -15,6 +15,12 @@ cudaError_t launch_rot_q8(const void *x, int x_dtype, long long x_stride, void *
                           int block, int mode, int out_hr, int scale_mode, int threads_target, int sms,
                           cudaStream_t stream);
 
+// Norm + modulation in front of the same tail. out_kind: 0 int8 codes + scales, 1 modulated fp32, 2 modulated fp16,
+// 3 rotated fp16. post != null selects the fused residual update (needs y); ln selects LayerNorm.
+cudaError_t launch_norm_mod_q8(float *x, long long x_stride, const float *mod, long long mod_stride,
+                               const unsigned char *rtype, void *out, float *sa, int M, int D, int block, float eps,
+                               int ln, int out_kind, const float *y, const float *post, cudaStream_t stream);
+
 // TMA-fed variant for bf16 / fp16 inputs of up to 16384 channels. `map` describes the input as
 // {64, cols / 64, M} with box {64, D / 64, 1} and 128-byte swizzle (built by the caller).
 bool rot_q8_tma_supported(int x_dtype, int D);

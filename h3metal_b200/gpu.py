@@ -61,6 +61,7 @@ def _signatures():
         "h3b_set_stream": (i32, [vp, vp]),
         "h3b_use_own_stream": (i32, [vp]),
         "h3b_rot_q8": (i32, [vp, vp, i32, i64, vp, vp, i32, i32, i32, i32, i32]),
+        "h3b_norm_mod_q8": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, ctypes.c_float, i32, i32, vp, vp]),
         "h3b_rot_amax": (i32, [vp, vp, i32, i64, vp, i32, i32, i32, i32]),
         "h3b_rot_q8_given_amax": (i32, [vp, vp, i32, i64, vp, vp, i32, i32, i32, i32]),
         "h3b_dequant_i32": (i32, [vp, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32]),
@@ -180,7 +181,7 @@ class Tensor:
 class Kernel:
     """One of the path's two kernels with the specialisation macros the caller asked for."""
 
-    SUPPORTED = {("gemm.metal", "gemm"), ("ops.metal", "rot_q8")}
+    SUPPORTED = {("gemm.metal", "gemm"), ("ops.metal", "rot_q8"), ("ops.metal", "norm_mod_q8")}
 
     def __init__(self, gpu: "Gpu", file: str, fn: str, macros: dict | None = None):
         if (file, fn) not in self.SUPPORTED:
@@ -282,6 +283,15 @@ class Gpu:
         if self._profile:
             self.names.append(name)
 
+    def norm_mod_q8_native(self, x: Tensor, x_stride: int, mod: Tensor, mod_stride: int, rtype: Tensor, out: Tensor,
+                           sa: Tensor | None, M: int, D: int, block: int, eps: float, ln: bool, out_kind: int,
+                           y: Tensor | None, post: Tensor | None, name: str = "norm_mod_q8"):
+        p = lambda t: t.ptr if t is not None else None  # noqa: E731
+        self._check(lib().h3b_norm_mod_q8(self.ctx, x.ptr, x_stride, mod.ptr, mod_stride, rtype.ptr, out.ptr, p(sa), M, D,
+                                           block, eps, int(ln), out_kind, p(y), p(post)))
+        if self._profile:
+            self.names.append(name)
+
     def rot_amax_native(self, x: Tensor, x_stride: int, amax: Tensor, M: int, D: int, block: int, mode: int):
         self._check(lib().h3b_rot_amax(self.ctx, x.ptr, _ABI_DTYPE[x.dtype], x_stride, amax.ptr, M, D, block, mode))
         if self._profile:
@@ -337,6 +347,15 @@ class Gpu:
                 x = x.view(x.shape, in_t)
             self.rot_q8_native(x, x_stride, out, sa, M, D, self.rot_block, mode, bool(int(k.macros.get("OUT_HR", 0))),
                                name=k.name)
+            return
+        if (k.file, k.fn) == ("ops.metal", "norm_mod_q8"):
+            M, D, x_stride, mod_stride, eps = struct.unpack("<4if", params)
+            x, mod, rtype, out, sa, _params, y, post = (list(args) + [None] * 8)[:8]
+            mac = k.macros
+            kind = 1 if int(mac.get("OUT_F", 0)) else 2 if int(mac.get("OUT_H", 0)) else 3 if int(mac.get("OUT_HR", 0)) else 0
+            self.norm_mod_q8_native(x, x_stride, mod, mod_stride, rtype, out, sa, M, D, self.rot_block, eps,
+                                    bool(int(mac.get("LN", 0))), kind, y if int(mac.get("POST", 0)) else None,
+                                    post if int(mac.get("POST", 0)) else None, name=k.name)
             return
         mac = k.macros
         if int(mac.get("WFMT", 1)) != 1 or int(mac.get("EPI", 0)) != 0:

@@ -5,7 +5,7 @@ and `LowRank` (:54-82) and the class `Scratch` (:37-47) keep their names, argume
 function enqueues its kernels on `gpu`; results are available after `gpu.wait()`.
 
 In scope: weight format "q8" with the storing epilogue (epi 0) and outputs bf16 / f16 / f32, with bias and with a
-low-rank (LoRA) term. Other formats and the gated-residual epilogue raise. `rot_q8` takes one argument the
+low-rank (LoRA) term; `norm_mod_q8` (:200-211), the other producer of int8 activations. Other formats and the gated-residual epilogue raise. `rot_q8` takes one argument the
 reference does not have, `block=` (the rotation block; the reference's kernel fixes it at 256).
 """
 
@@ -171,6 +171,23 @@ def gemm(gpu: Gpu, a: Tensor, wt: QWeight, out: Tensor, M: int, *, sa: Tensor | 
     gpu.gemm_native(a, a_stride or wt.K, wt.w, wt.w_stride, wt.sw, sa, wt.bias, out, out.dtype, c_stride or wt.N,
                     m_pad, wt.N, wt.K, lt, t_stride, lb, b_stride, R, ranges_ptr,
                     name=f"gemm(q8,{wt.K}->{wt.N}{',lora' if _low is not None else ''})")
+
+
+def norm_mod_q8(gpu: Gpu, x: Tensor, mod: Tensor, rtype: Tensor, out: Tensor, sa: Tensor | None, M: int, D: int,
+                *, eps: float, mod_stride: int | None = None, x_stride: int | None = None, out_f: bool = False,
+                out_h: bool = False, out_hr: bool = False, y: Tensor | None = None, post: Tensor | None = None,
+                ln: bool = False, block: int = RB):
+    """out = int8(rot(rmsnorm(x) * mod[type][0] + mod[type][1])) and its row scales (or the plain modulated row as
+    float with out_f, as half with out_h, the rotated row as half with out_hr). With y and post, first
+    x += post * rmsnorm(y) (same eps), written back. ln: LayerNorm without affine (mean subtracted) instead of
+    RMSNorm. Same signature as the reference's h3metal/ops.py:200-211 plus block=."""
+    if D % block:
+        raise ValueError(f"norm_mod_q8: {D} channels are not a multiple of the rotation block {block}")
+    if (y is None) != (post is None):
+        raise ValueError("norm_mod_q8: y and post go together")
+    kind = 1 if out_f else 2 if out_h else 3 if out_hr else 0
+    gpu.norm_mod_q8_native(x, x_stride or D, mod, mod_stride or 2 * D, rtype, out, sa, M, D, block, eps, ln, kind, y,
+                           post, name=f"norm_mod_q8({D},b{block}{',ln' if ln else ''}{',post' if post is not None else ''})")
 
 
 def rot_q8(gpu: Gpu, x: Tensor, out: Tensor, sa: Tensor | None, M: int, D: int, *, swiglu: bool = False,

@@ -72,6 +72,21 @@ H3B_API int h3b_use_own_stream(h3b_ctx *ctx);
 H3B_API int h3b_rot_q8(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, float *sa, int M, int D,
                int block, int mode, int out_hr);
 
+/* RMSNorm (or LayerNorm without affine) + modulation + the same rotate + quantise tail, in one pass over the fp32
+ * residual stream. Replaces the dispatch of the Metal kernel norm_mod_q8 (kernels/ops.metal:111-268; parameter block
+ * NormQParams kernels/params.h:18-23; launcher h3metal/ops.py:200-211; buffers x, mod, rtype, out, sa, params, y, post).
+ *   x      fp32 [M][x_stride]; with post it is updated in place: x[m] += post * rmsnorm(y[m])
+ *   mod    fp32, per row type D scale' values then D shift values; rows mod_stride (>= 2 D) apart
+ *   rtype  one byte per row: the row's type
+ *   out    out_kind 0: int8 [M][D] with row scales in sa; 1: fp32 [M][D] = norm(x) * scale' + shift (no rotation);
+ *          2: the same as fp16; 3: the rotated row as fp16
+ *   ln     non-zero: subtract the row mean first (LayerNorm); excludes post
+ *   y, post  both or neither: fp32 [M][D] and fp32 [D]
+ * D must be a multiple of block (64, 128, 256). All tensors 16-byte aligned, strides multiples of 16 bytes. */
+H3B_API int h3b_norm_mod_q8(h3b_ctx *ctx, float *x, int64_t x_stride, const float *mod, int64_t mod_stride,
+                            const uint8_t *rtype, void *out, float *sa, int M, int D, int block, float eps, int ln,
+                            int out_kind, const float *y, const float *post);
+
 /* The two halves of h3b_rot_q8 for a row whose channels are sharded over several GPUs (a K-sharded, "row-parallel"
  * layer): the reference quantises with ONE scale per token taken over the whole row (kernels/ops.metal:315-317), so
  * each GPU first reports the largest rotated magnitude of its shard, the host reduces those with MAX over the GPUs,

@@ -24,4 +24,5 @@ butterfly (oracle/rotq8_witness.c).
 from .quant_ref import (bf16_round_bits, bf16_bits_to_f32, hadamard, random_signs, rotate_in, quant_q8,
                         dequant_q8)
 from .rotq8_ref import rot_q8_rows, rotate_rows_matmul
+from .normq8_ref import norm_mod_rows
 from .gemm_ref import int32_product, epilogue_q8, gemm_q8, low_rank_ref, lora_table, lora_T, LowRankRef

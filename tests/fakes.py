@@ -55,6 +55,11 @@ class RecordingGpu:
                                out=out, out_dtype=out_dtype, c_stride=c_stride, M=M, N=N, K=K, lt=lt,
                                t_stride=t_stride, lb=lb, b_stride=b_stride, R=R, ranges_ptr=ranges_ptr))
 
+    def norm_mod_q8_native(self, x, x_stride, mod, mod_stride, rtype, out, sa, M, D, block, eps, ln, out_kind, y, post,
+                           name="norm_mod_q8"):
+        self.calls.append(dict(kind="norm_mod_q8", x=x, x_stride=x_stride, mod=mod, mod_stride=mod_stride, rtype=rtype,
+                               out=out, sa=sa, M=M, D=D, block=block, eps=eps, ln=ln, out_kind=out_kind, y=y, post=post))
+
     def rot_q8_native(self, x, x_stride, out, sa, M, D, block, mode, out_hr, name="rot_q8"):
         self.calls.append(dict(kind="rot_q8", x=x, x_stride=x_stride, out=out, sa=sa, M=M, D=D, block=block,
                                mode=mode, out_hr=out_hr))

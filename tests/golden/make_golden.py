@@ -111,6 +111,19 @@ def main():
     out["rot_expect_plain_f64"] = ref_test_ops.rot(xf[:, :768])
     out["rot_expect_swiglu_f64"] = ref_test_ops.rot(xf[:, :768] * g / (1 + np.exp(-g)))
 
+    # -- tests/test_ops.py:28-53 (test_norm_mod): the float64 expectation the reference's test builds, RMS and LN ---------
+    for tag, ln in (("rms", False), ("ln", True)):
+        r2 = np.random.default_rng(1)
+        xn_in = (r2.standard_normal((6, 768)) * 3 + (50 if ln else 0)).astype(np.float32)
+        nmod = r2.standard_normal((3, 2, 768)).astype(np.float32)
+        nrt = r2.integers(0, 3, size=6).astype(np.uint8)
+        xc = xn_in.astype(np.float64) - (xn_in.astype(np.float64).mean(1, keepdims=True) if ln else 0)
+        xn = xc / np.sqrt((xc ** 2).mean(1, keepdims=True) + 1e-5)
+        yy = xn * nmod[nrt, 0] + nmod[nrt, 1]
+        out[f"norm_{tag}_x"], out[f"norm_{tag}_mod"], out[f"norm_{tag}_rt"] = xn_in, nmod, nrt
+        out[f"norm_{tag}_expect_y_f64"] = yy
+        out[f"norm_{tag}_expect_rot_f64"] = ref_test_ops.rot(yy)
+
     np.savez_compressed(os.path.join(HERE, "ref_golden.npz"), **out)
     print("wrote", len(out), "arrays,", os.path.getsize(os.path.join(HERE, "ref_golden.npz")), "bytes;",
           len(dispatch), "dispatches")

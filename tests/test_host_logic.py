@@ -114,3 +114,18 @@ def test_gemm_refusals():
     assert not g.calls
     ops.gemm(g, a, wt, out, 40, sa=sa)
     assert g.calls[0]["M"] == 64 and ops.pad_rows(129) == 256  # rows padded to the tile height, all written
+
+
+def test_norm_mod_q8_parameters():
+    """Defaults of the reference's launcher (h3metal/ops.py:200-211): x_stride = D, mod_stride = 2 D; variants map to
+    one output kind; y and post go together."""
+    g = RecordingGpu()
+    x, mod, rt = g.empty((8, 768), "f32"), g.empty((3, 2, 768), "f32"), g.empty((8,), "u8")
+    out, sa = g.empty((8, 768), "i8"), g.empty((8,), "f32")
+    ops.norm_mod_q8(g, x, mod, rt, out, sa, 8, 768, eps=1e-5)
+    ops.norm_mod_q8(g, x, mod, rt, out, None, 8, 768, eps=1e-5, out_hr=True, ln=True, block=128, x_stride=1024)
+    a, b = g.calls
+    assert (a["x_stride"], a["mod_stride"], a["block"], a["out_kind"], a["ln"]) == (768, 1536, 256, 0, False)
+    assert (b["x_stride"], b["block"], b["out_kind"], b["ln"]) == (1024, 128, 3, True)
+    with pytest.raises(ValueError):
+        ops.norm_mod_q8(g, x, mod, rt, out, sa, 8, 768, eps=1e-5, post=mod)
