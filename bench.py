@@ -214,6 +214,7 @@ def run_ours(args, cfg, rank, world):
     import torch
     import torch.distributed as dist
     from h3metal_b200.gpu import Gpu
+    from h3metal_b200 import ops as ops_mod
     from h3metal_b200.linear import BlockLinears
 
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -335,6 +336,24 @@ def run_ours(args, cfg, rank, world):
         e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "ms_per_step": e2e_ms / args.steps}
 
+    # ---- the other producer of int8 activations, norm_mod_q8, at the block's hidden size (not part of the step) ----
+    hidden = blk.layers[0].wt.K
+    xres = torch.randn(blk.layers[0].m_pad, hidden, device=dev) * 3
+    modt = torch.randn(3, 2, hidden, device=dev)
+    rtt = torch.randint(0, 3, (blk.layers[0].m_pad,), device=dev, dtype=torch.uint8)
+    X32, MODT, RTT = gpu.wrap(xres), gpu.wrap(modt), gpu.wrap(rtt)
+    l0 = blk.layers[0]
+
+    def norm_step():
+        ops_mod.norm_mod_q8(gpu, X32, MODT, RTT, l0.a8, l0.sa, blk.M, hidden, eps=1e-5, block=cfg.block)
+
+    for _ in range(3):
+        norm_step()
+    norm_ms = timed(norm_step, args.steps) / args.steps
+    norm_bytes = blk.M * (4 * hidden + hidden + 4)
+    norm_extra = {"kernel": "norm_mod_q8_kernel", "rows": blk.M, "channels": hidden, "us": norm_ms * 1e3,
+                  "achieved_gbs": norm_bytes / (norm_ms * 1e-3) / 1e9, "frac_of_measured_hbm": norm_bytes / (norm_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+
     if world > 1:
         dist.barrier()
     if rank != 0:
@@ -348,7 +367,7 @@ def run_ours(args, cfg, rank, world):
                          f"{sum(2 * l.m_pad * (l.wt.K + l.wt.N) for l in blk.layers) / 1e9:.2f} GB of activations and outputs) "
                          f"exceeds the 126 MB L2"},
         "tops": value / cfg.M * cfg.ops / 1e12 ,
-        "roofline": roofline, "roofline_rot_q8": roofline_rot,
+        "roofline": roofline, "roofline_rot_q8": roofline_rot, "norm_mod_q8": norm_extra,
         "e2e": e2e,
         "gpu_launches": int(launches),
         "clocks": dict(clocks.summary(), window=f"timed region + {extra_steps} identical steps run straight after it"),

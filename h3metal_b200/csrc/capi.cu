@@ -391,7 +391,8 @@ int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int /*lora*/) {
 static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
                         const float *sw, const float *sa, const float *bias, void *C, int c_dtype, int64_t c_stride,
                         int M, int N, int K, const void *lora_T, int64_t t_stride, const void *lora_B,
-                        int64_t b_stride, int R, const int32_t *lora_ranges, bool cached_maps) {
+                        int64_t b_stride, int R, const int32_t *lora_ranges, bool cached_maps,
+                        const uint8_t *rtype = nullptr, const float *gate = nullptr, int64_t g_stride = 0) {
   if (!ctx) return fail("null context");
   if (!A || !W || !C) return fail("gemm: null tensor argument");
   if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: M, N and K must be positive");
@@ -434,6 +435,12 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
     if (!(m = ctx->map2(cached_maps, &local, lora_B, h3b::kDtypeF16, R, N, b_stride * 2, 32, bn, 64))) return -1;
     g.map_b = *m;
   }
+  if (gate != nullptr) {
+    if (!rtype) return fail("gemm: the gated-residual epilogue needs the row types");
+    if (c_dtype != H3B_F32) return fail("gemm: the gated-residual epilogue accumulates into an fp32 residual stream");
+    if (g_stride < N) return fail("gemm: g_stride smaller than N");
+  }
+  g.rtype = rtype; g.gate = gate; g.g_stride = g_stride;
   g.sw = sw; g.sa = sa; g.bias = raw ? nullptr : bias; g.c = C; g.ranges = lora ? lora_ranges : nullptr;
   g.c_stride = c_stride; g.c_dtype = c_dtype; g.M = M; g.N = N; g.K = K; g.R = lora ? R : 0; g.bn = bn;
   g.acc_stages = (lora && bn == 256) ? 1 : 2;
@@ -469,6 +476,15 @@ int h3b_gemm_w8a8(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t 
                   int R, const int32_t *lora_ranges) {
   return gemm_enqueue(ctx, A, a_stride, W, w_stride, sw, sa, bias, C, c_dtype, c_stride, M, N, K, lora_T, t_stride,
                       lora_B, b_stride, R, lora_ranges, true);
+}
+
+int h3b_gemm_w8a8_gated(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
+                        const float *sw, const float *sa, const float *bias, float *X, int64_t c_stride, int M, int N,
+                        int K, const uint8_t *rtype, const float *gate, int64_t g_stride, const void *lora_T,
+                        int64_t t_stride, const void *lora_B, int64_t b_stride, int R, const int32_t *lora_ranges) {
+  if (!gate) return fail("gemm (gated): null gate table");
+  return gemm_enqueue(ctx, A, a_stride, W, w_stride, sw, sa, bias, X, H3B_F32, c_stride, M, N, K, lora_T, t_stride, lora_B,
+                      b_stride, R, lora_ranges, true, rtype, gate, g_stride);
 }
 
 // ---- the product with a LoRA term for callers that cannot allocate ------------------------------------------------

@@ -100,7 +100,9 @@ __device__ __forceinline__ void store_segment(OUT_T *dst, const float (&v)[32], 
 }
 
 // Finishes 32 accumulator columns [n, n + 32) of row m: either the raw int32 values, or the dequantising
-// epilogue float(acc) * sa * sw (+ bias) (+ low) in the reference's operation order, converted to the output type.
+// epilogue float(acc) * sa * sw (+ bias) (+ low) in the reference's operation order, converted to the output type
+// or, with a gate table, accumulated into the fp32 residual stream (the reference's epilogue 1,
+// kernels/gemm.metal:18-20,256-259).
 // sw_s / bias_s point at the tile's staged column scales and biases for these 32 columns.
 __device__ __forceinline__ void finish_chunk(const GemmLaunch &g, const uint32_t (&acc)[32], const uint32_t (&low)[32],
                                              bool has_low, int m, int n, float sa_m, const float *sw_s,
@@ -145,6 +147,27 @@ __device__ __forceinline__ void finish_chunk(const GemmLaunch &g, const uint32_t
     v[j] = x0.x; v[j + 1] = x0.y; v[j + 2] = x1.x; v[j + 3] = x1.y;
   }
   const size_t off = static_cast<size_t>(m) * g.c_stride + n;
+  if (g.gate != nullptr) {
+    // gated-residual epilogue: X[m][n] += gate[type[m]][n] * v, X the fp32 residual stream (one multiply, one add)
+    float *x = static_cast<float *>(g.c) + off;
+    const float *gr = g.gate + static_cast<size_t>(g.rtype[m]) * g.g_stride + n;
+    if (vec_ok && n_valid >= 32 && (reinterpret_cast<uintptr_t>(gr) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 x4 = *reinterpret_cast<const float4 *>(x + j);
+        const float4 g4 = __ldg(reinterpret_cast<const float4 *>(gr + j));
+        *reinterpret_cast<float4 *>(x + j) =
+            make_float4(__fadd_rn(x4.x, __fmul_rn(g4.x, v[j])), __fadd_rn(x4.y, __fmul_rn(g4.y, v[j + 1])),
+                        __fadd_rn(x4.z, __fmul_rn(g4.z, v[j + 2])), __fadd_rn(x4.w, __fmul_rn(g4.w, v[j + 3])));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < n_valid) x[j] = __fadd_rn(x[j], __fmul_rn(__ldg(gr + j), v[j]));
+      }
+    }
+    return;
+  }
   if (g.c_dtype == kDtypeBf16) store_segment(static_cast<__nv_bfloat16 *>(g.c) + off, v, n_valid, vec_ok);
   else if (g.c_dtype == kDtypeF16) store_segment(static_cast<__half *>(g.c) + off, v, n_valid, vec_ok);
   else store_segment(static_cast<float *>(g.c) + off, v, n_valid, vec_ok);

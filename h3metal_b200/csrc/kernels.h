@@ -48,6 +48,9 @@ struct GemmLaunch {
   const float *bias;   // [N] or null
   void *c;             // [M][c_stride] of c_dtype
   const int *ranges;   // (k0, k1) per BN-wide column tile, or null for the whole rank range
+  const unsigned char *rtype;  // gated-residual epilogue: one type byte per row, else null
+  const float *gate;   // gated-residual epilogue: fp32 [types][g_stride]
+  long long g_stride;
   long long c_stride;
   int c_dtype;         // kDtypeBf16 / kDtypeF16 / kDtypeF32, or kDtypeI32 for the raw accumulators
   int M, N, K;

@@ -67,6 +67,8 @@ def _signatures():
         "h3b_dequant_i32": (i32, [vp, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32]),
         "h3b_gemm_w8a8": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32, i32, vp, i64, vp, i64, i32,
                                 vp]),
+        "h3b_gemm_w8a8_gated": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, vp, i64, i32, i32, i32, vp, vp, i64, vp, i64, vp, i64,
+                                      i32, vp]),
         "h3b_gemm_w8a8_lora_noalloc": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32, i32, vp, i64, vp,
                                              vp, i64, i32, vp]),
         "h3b_gemm_tile_n": (i32, [vp, i32, i32]),
@@ -323,6 +325,18 @@ class Gpu:
         if self._profile:
             self.names.append(name)
 
+    def gemm_gated_native(self, a: Tensor, a_stride: int, w: Tensor, w_stride: int, sw: Tensor, sa: Tensor,
+                          bias: Tensor | None, x: Tensor, c_stride: int, M: int, N: int, K: int, rtype: Tensor,
+                          gate: Tensor, g_stride: int, lt: Tensor | None = None, t_stride: int = 0,
+                          lb: Tensor | None = None, b_stride: int = 0, R: int = 0, ranges_ptr: int | None = None,
+                          name: str = "gemm(epi1)"):
+        p = lambda t: t.ptr if t is not None else None  # noqa: E731
+        self._check(lib().h3b_gemm_w8a8_gated(self.ctx, a.ptr, a_stride, w.ptr, w_stride, sw.ptr, sa.ptr, p(bias), x.ptr,
+                                               c_stride, M, N, K, rtype.ptr, gate.ptr, g_stride, p(lt), t_stride, p(lb),
+                                               b_stride, R, ranges_ptr))
+        if self._profile:
+            self.names.append(name)
+
     def gemm_tile_n(self, N: int, lora: bool) -> int:
         return lib().h3b_gemm_tile_n(self.ctx, N, int(lora))
 
@@ -358,8 +372,9 @@ class Gpu:
                                     post if int(mac.get("POST", 0)) else None, name=k.name)
             return
         mac = k.macros
-        if int(mac.get("WFMT", 1)) != 1 or int(mac.get("EPI", 0)) != 0:
-            raise GpuError("gemm: only the int8 weight format (WFMT 1) with the storing epilogue (EPI 0) exists here")
+        if int(mac.get("WFMT", 1)) != 1:
+            raise GpuError("gemm: only the int8 weight format (WFMT 1) exists here")
+        epi1 = int(mac.get("EPI", 0)) == 1
         M, N, K, a_stride, c_stride, w_stride, _groups, _g_stride = struct.unpack("<8i", params)
         a, w, sw, sa, out, bias = (list(args) + [None] * 6)[:6]
         out_dtype = _METAL_T[str(mac.get("OUT_T", "half"))]
@@ -375,12 +390,16 @@ class Gpu:
             head = lr.numpy()[:2]
             R = int(head[0])
             ranges_ptr = lr.ptr + 8
-            self.gemm_native(a, a_stride, w, w_stride, sw, sa, bias if int(mac.get("HAS_BIAS", 0)) else None, out,
-                             out_dtype, c_stride, M, N, K, lt, int(head[0]), lb, int(head[1]), R, ranges_ptr,
+            lora_args = (lt, int(head[0]), lb, int(head[1]), R, ranges_ptr)
+        else:
+            lora_args = (None, 0, None, 0, 0, None)
+        b = bias if int(mac.get("HAS_BIAS", 0)) else None
+        if epi1:
+            self.gemm_gated_native(a, a_stride, w, w_stride, sw, sa, b, out, c_stride, M, N, K, args[6], args[7],
+                                   _g_stride, *lora_args, name=k.name)
+        else:
+            self.gemm_native(a, a_stride, w, w_stride, sw, sa, b, out, out_dtype, c_stride, M, N, K, *lora_args,
                              name=k.name)
-            return
-        self.gemm_native(a, a_stride, w, w_stride, sw, sa, bias if int(mac.get("HAS_BIAS", 0)) else None, out,
-                         out_dtype, c_stride, M, N, K, name=k.name)
 
     _profile = False
 

@@ -4,8 +4,8 @@
 and `LowRank` (:54-82) and the class `Scratch` (:37-47) keep their names, arguments and error behaviour. Each
 function enqueues its kernels on `gpu`; results are available after `gpu.wait()`.
 
-In scope: weight format "q8" with the storing epilogue (epi 0) and outputs bf16 / f16 / f32, with bias and with a
-low-rank (LoRA) term; `norm_mod_q8` (:200-211), the other producer of int8 activations. Other formats and the gated-residual epilogue raise. `rot_q8` takes one argument the
+In scope: weight format "q8" with the storing epilogue (epi 0; outputs bf16 / f16 / f32) and the gated-residual
+epilogue (epi 1, with ksplit), with bias and with a low-rank (LoRA) term; `norm_mod_q8` (:200-211), the other producer of int8 activations. Other weight formats raise. `rot_q8` takes one argument the
 reference does not have, `block=` (the rotation block; the reference's kernel fixes it at 256).
 """
 
@@ -129,19 +129,24 @@ def pad_rows(m: int, tile: int = 128) -> int:
 def gemm(gpu: Gpu, a: Tensor, wt: QWeight, out: Tensor, M: int, *, sa: Tensor | None = None, epi: int = 0,
          rtype: Tensor | None = None, gate: Tensor | None = None, g_stride: int = 0, c_stride: int | None = None,
          a_stride: int | None = None, tile=(64, 128, 4), swz: int = 1, ksplit: int = 1, _low=None):
-    """out = A x W^T (epi 0): int8 x int8 with int32 accumulation, then out_dtype(acc * sa[m] * sw[n] + bias[n] + low).
+    """out = A x W^T (epi 0), or out += gate[rtype] * (A x W^T) (epi 1, out the fp32 residual stream): int8 x int8
+    with int32 accumulation, then acc * sa[m] * sw[n] + bias[n] + low.
 
-    A weight with a low-rank term (wt.low) first computes the term's input side T from the same activations,
-    then adds T B^T inside the main product's epilogue. `tile` keeps its checking role (its width must divide N,
-    and rows are padded to its height, all of which are written); the kernel picks its own tile shape. `swz` is
-    accepted and ignored (the kernel has its own L2-friendly tile order).
+    ksplit: accumulate the product in that many calls over consecutive slices of K (epi 1 only; the bias and the
+    low-rank term join the first slice), exactly the sequence the reference runs. A weight with a low-rank term
+    (wt.low) first computes the term's input side T from the same activations, then adds T B^T inside the main
+    product's epilogue. `tile` keeps its checking role (its width must divide N, and rows are padded to its height,
+    all of which are written); the kernel picks its own tile shape. `swz` is accepted and ignored (the kernel has
+    its own L2-friendly tile order).
     """
     if wt.fmt != "q8":
         raise NotImplementedError(f"gemm: weight format {wt.fmt!r} is outside this library (int8 'q8' only)")
-    if epi != 0:
-        raise NotImplementedError("gemm: only the storing epilogue (epi 0) is implemented")
+    if epi not in (0, 1):
+        raise NotImplementedError(f"gemm: epilogue {epi}")
     if sa is None:
         raise ValueError("gemm: int8 activations need their row scales (sa)")
+    if epi == 1 and (rtype is None or gate is None):
+        raise ValueError("gemm: the gated-residual epilogue needs rtype and gate")
     if wt.low is not None:
         lo = wt.low
         # T covers the rows of the whole 128-row tiles the activations are allocated in
@@ -151,10 +156,21 @@ def gemm(gpu: Gpu, a: Tensor, wt: QWeight, out: Tensor, M: int, *, sa: Tensor | 
         _low = (t, lo)
         wt = replace(wt, low=None)
     if ksplit > 1:
-        raise ValueError(f"cannot split K of a {wt.fmt} product (epi {epi}, K {wt.K}) {ksplit} ways")
+        if epi != 1 or wt.K % (ksplit * 256):
+            raise ValueError(f"cannot split K of a {wt.fmt} product (epi {epi}, K {wt.K}) {ksplit} ways")
+        kp = wt.K // ksplit
+        for i in range(ksplit):
+            part = replace(wt, w=wt.w.view((wt.N, kp), offset_elems=i * kp), K=kp, ws=wt.w_stride,
+                           bias=wt.bias if i == 0 else None)
+            gemm(gpu, a.view((a.shape[0], kp), offset_elems=i * kp), part, out, M, sa=sa, epi=1, rtype=rtype, gate=gate,
+                 g_stride=g_stride, c_stride=c_stride, a_stride=a_stride or wt.K, tile=tile, swz=swz,
+                 _low=_low if i == 0 else None)
+        return
     tm, tn, _nsg = tile
     if wt.N % tn:
         raise ValueError(f"gemm tile {tile}: {tn} columns do not divide the product's {wt.N}")
+    if epi == 1 and out.dtype != "f32":
+        raise ValueError("gemm: the gated-residual epilogue accumulates into an fp32 tensor")
     if out.dtype not in OUT_DT and out.dtype != "i32":
         raise ValueError(f"gemm: output type {out.dtype}")
     m_pad = (M + tm - 1) // tm * tm
@@ -168,9 +184,14 @@ def gemm(gpu: Gpu, a: Tensor, wt: QWeight, out: Tensor, M: int, *, sa: Tensor | 
         lb = lo.b
         R = t_stride = b_stride = lo.R
         ranges_ptr = lo.table(gpu, gpu.gemm_tile_n(wt.N, True)).ptr + 8  # skip the table's two leading strides
+    tag = f"gemm(q8,{wt.K}->{wt.N}{',lora' if _low is not None else ''}{',epi1' if epi else ''})"
+    if epi == 1:
+        gpu.gemm_gated_native(a, a_stride or wt.K, wt.w, wt.w_stride, wt.sw, sa, wt.bias, out, c_stride or wt.N, m_pad,
+                              wt.N, wt.K, rtype, gate, g_stride or wt.N, lt, t_stride, lb, b_stride, R, ranges_ptr,
+                              name=tag)
+        return
     gpu.gemm_native(a, a_stride or wt.K, wt.w, wt.w_stride, wt.sw, sa, wt.bias, out, out.dtype, c_stride or wt.N,
-                    m_pad, wt.N, wt.K, lt, t_stride, lb, b_stride, R, ranges_ptr,
-                    name=f"gemm(q8,{wt.K}->{wt.N}{',lora' if _low is not None else ''})")
+                    m_pad, wt.N, wt.K, lt, t_stride, lb, b_stride, R, ranges_ptr, name=tag)
 
 
 def norm_mod_q8(gpu: Gpu, x: Tensor, mod: Tensor, rtype: Tensor, out: Tensor, sa: Tensor | None, M: int, D: int,

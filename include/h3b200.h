@@ -126,6 +126,17 @@ H3B_API int h3b_gemm_w8a8(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const
                   int M, int N, int K, const void *lora_T, int64_t t_stride, const void *lora_B, int64_t b_stride,
                   int R, const int32_t *lora_ranges);
 
+/* The same product with the reference's second epilogue (EPI 1, kernels/gemm.metal:18-20,256-259; launcher
+ * h3metal/ops.py:124-174 with epi=1): instead of storing, it accumulates into the fp32 residual stream,
+ *   X[m][n] += gate[rtype[m]][n] * (float(acc) * sa[m] * sw[n] + bias[n] + low[m][n])
+ * X fp32 [M][c_stride]; rtype one byte per row; gate fp32 [types][g_stride]. Other arguments as h3b_gemm_w8a8.
+ * K may be split by the caller into consecutive slices accumulated by successive calls (the reference's ksplit). */
+H3B_API int h3b_gemm_w8a8_gated(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
+                                const float *sw, const float *sa, const float *bias, float *X, int64_t c_stride, int M,
+                                int N, int K, const uint8_t *rtype, const float *gate, int64_t g_stride,
+                                const void *lora_T, int64_t t_stride, const void *lora_B, int64_t b_stride, int R,
+                                const int32_t *lora_ranges);
+
 /* The product with a LoRA term for callers that cannot allocate device memory. It has no counterpart in the
  * reference (whose Scratch object, h3metal/ops.py:37-47, simply grows a buffer on demand).
  *

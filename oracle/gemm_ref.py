@@ -41,6 +41,13 @@ def epilogue_q8(acc: np.ndarray, sa: np.ndarray, sw: np.ndarray, bias: np.ndarra
     return v
 
 
+def accumulate_gated(x: np.ndarray, v: np.ndarray, gate: np.ndarray, rtype: np.ndarray) -> np.ndarray:
+    """Epilogue 1: X[m][n] += gate[type[m]][n] * v (kernels/gemm.metal:18-20,256-259), fp32 multiply then fp32 add;
+    v already holds the bias and the low-rank term. Returns the new X."""
+    t = (gate.astype(np.float32)[rtype] * v.astype(np.float32)).astype(np.float32)
+    return (x.astype(np.float32) + t).astype(np.float32)
+
+
 def store_as(v: np.ndarray, dtype: str) -> np.ndarray:
     """OUT_T(v) (kernels/gemm.metal:254-255): bf16 bit patterns (uint16), fp16 or fp32."""
     if dtype == "bf16":

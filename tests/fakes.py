@@ -39,7 +39,7 @@ class RecordingGpu:
     def upload(self, arr, dtype=None):
         arr = np.ascontiguousarray(arr)
         dtype = dtype or {np.dtype(np.float32): "f32", np.dtype(np.float16): "f16", np.dtype(np.int8): "i8",
-                          np.dtype(np.int32): "i32", np.dtype(np.uint16): "bf16"}[arr.dtype]
+                          np.dtype(np.int32): "i32", np.dtype(np.uint16): "bf16", np.dtype(np.uint8): "u8"}[arr.dtype]
         t = self.empty(arr.shape, dtype)
         t.numpy()[...] = arr.view(gpu_mod._NP[dtype]).reshape(t.shape)
         return t
@@ -54,6 +54,11 @@ class RecordingGpu:
         self.calls.append(dict(kind="gemm", a=a, a_stride=a_stride, w=w, w_stride=w_stride, sw=sw, sa=sa, bias=bias,
                                out=out, out_dtype=out_dtype, c_stride=c_stride, M=M, N=N, K=K, lt=lt,
                                t_stride=t_stride, lb=lb, b_stride=b_stride, R=R, ranges_ptr=ranges_ptr))
+
+    def gemm_gated_native(self, a, a_stride, w, w_stride, sw, sa, bias, x, c_stride, M, N, K, rtype, gate, g_stride,
+                          lt=None, t_stride=0, lb=None, b_stride=0, R=0, ranges_ptr=None, name="gemm(epi1)"):
+        self.calls.append(dict(kind="gemm_gated", a=a, a_stride=a_stride, w=w, w_stride=w_stride, bias=bias, out=x,
+                               c_stride=c_stride, M=M, N=N, K=K, g_stride=g_stride, lt=lt, R=R))
 
     def norm_mod_q8_native(self, x, x_stride, mod, mod_stride, rtype, out, sa, M, D, block, eps, ln, out_kind, y, post,
                            name="norm_mod_q8"):

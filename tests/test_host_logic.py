@@ -104,9 +104,11 @@ def test_gemm_refusals():
     wt = ops.QWeight("q8", g.upload(np.zeros((256, 512), np.int8)), g.upload(np.ones(256, np.float32)), 256, 512)
     a, sa, out = g.upload(np.zeros((64, 512), np.int8)), g.upload(np.ones(64, np.float32)), g.empty((64, 256), "f16")
     with pytest.raises(ValueError):
-        ops.gemm(g, a, wt, out, 64, sa=sa, ksplit=2)
-    with pytest.raises(NotImplementedError):
-        ops.gemm(g, a, wt, out, 64, sa=sa, epi=1)
+        ops.gemm(g, a, wt, out, 64, sa=sa, ksplit=2)          # K splits exist for the accumulating epilogue only
+    with pytest.raises(ValueError):
+        ops.gemm(g, a, wt, out, 64, sa=sa, epi=1)             # needs rtype and gate
+    with pytest.raises(ValueError):
+        ops.gemm(g, a, wt, out, 64, sa=sa, epi=1, rtype=sa, gate=sa)  # fp16 out: the residual stream is fp32
     with pytest.raises(NotImplementedError):
         ops.gemm(g, a, ops.QWeight("q4", wt.w, wt.sw, 256, 512), out, 64, sa=sa)
     with pytest.raises(ValueError):
@@ -129,3 +131,22 @@ def test_norm_mod_q8_parameters():
     assert (b["x_stride"], b["block"], b["out_kind"], b["ln"]) == (1024, 128, 3, True)
     with pytest.raises(ValueError):
         ops.norm_mod_q8(g, x, mod, rt, out, sa, 8, 768, eps=1e-5, post=mod)
+
+
+def test_k_split_sequence_matches_the_reference():
+    """h3metal/ops.py:143-154: ksplit slices of K, each a view of the whole operands (a_stride = w_stride = K), the
+    bias and the low-rank term on the first slice only; refused when K is not a multiple of ksplit * 256."""
+    g = RecordingGpu()
+    N, K = 256, 1024
+    wt = ops.QWeight("q8", g.upload(np.zeros((N, K), np.int8)), g.upload(np.ones(N, np.float32)), N, K,
+                     bias=g.upload(np.zeros(N, np.float32)))
+    a, sa = g.upload(np.zeros((128, K), np.int8)), g.upload(np.ones(128, np.float32))
+    x = g.empty((128, N), "f32")
+    rt, gate = g.upload(np.zeros(128, np.uint8)), g.upload(np.ones((3, N), np.float32))
+    ops.gemm(g, a, wt, x, 100, sa=sa, epi=1, rtype=rt, gate=gate, ksplit=2)
+    first, second = g.calls
+    assert (first["K"], first["a_stride"], first["w_stride"], first["M"]) == (512, 1024, 1024, 128)
+    assert first["a"].ptr == a.ptr and second["a"].ptr == a.ptr + 512 and second["w"].ptr == wt.w.ptr + 512
+    assert first["bias"] is not None and second["bias"] is None and first["g_stride"] == N
+    with pytest.raises(ValueError):
+        ops.gemm(g, a, wt, x, 100, sa=sa, epi=1, rtype=rt, gate=gate, ksplit=3)
