@@ -151,7 +151,8 @@ struct h3b_ctx {
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt = key.dtype == h3b::kDtypeI8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : key.dtype == h3b::kDtypeBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+                                 : key.dtype == h3b::kDtypeF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUtensorMapSwizzle sw = key.swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     const CUresult r = encode(out, dt, static_cast<cuuint32_t>(key.rank), const_cast<void *>(key.ptr), dims, strides, box,
                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -346,6 +347,17 @@ int h3b_norm_mod_q8(h3b_ctx *ctx, float *x, int64_t x_stride, const float *mod, 
       (y && reinterpret_cast<uintptr_t>(y) % 16) || (post && reinterpret_cast<uintptr_t>(post) % 16))
     return fail("norm_mod_q8: tensors must be 16-byte aligned with row strides that are multiples of 16 bytes");
   cudaEvent_t ps = nullptr;
+  if (!post && ctx->rot_stages >= 0 && h3b::norm_mod_q8_tma_supported(D)) {
+    // rows reach shared memory by TMA: x seen as {32 floats, x_stride / 32 lines, M rows}
+    const CUtensorMap *map = ctx->tensor_map3(x, h3b::kDtypeF32, 32, static_cast<uint64_t>(D) / 32, M, 128,
+                                              static_cast<uint64_t>(x_stride) * 4, 32, static_cast<uint32_t>(D / 32), 128);
+    if (!map) return -1;
+    if (ctx->before_launch(&ps)) return -1;
+    const cudaError_t e = h3b::launch_norm_mod_q8_tma(*map, mod, mod_stride, rtype, out, sa, M, D, block, eps, ln, out_kind,
+                                                      ctx->rot_stages, ctx->prop.multiProcessorCount, ctx->status_dev,
+                                                      ctx->stream);
+    return ctx->after_launch("norm_mod_q8 launch", e);
+  }
   if (ctx->before_launch(&ps)) return -1;
   const cudaError_t e = h3b::launch_norm_mod_q8(x, x_stride, mod, mod_stride, rtype, out, sa, M, D, block, eps, ln, out_kind,
                                                 y, post, ctx->stream);

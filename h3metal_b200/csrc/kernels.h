@@ -24,11 +24,15 @@ cudaError_t launch_norm_mod_q8(float *x, long long x_stride, const float *mod, l
 // TMA-fed variant for bf16 / fp16 inputs of up to 16384 channels. `map` describes the input as
 // {64, cols / 64, M} with box {64, D / 64, 1} and 128-byte swizzle (built by the caller).
 bool rot_q8_tma_supported(int x_dtype, int D);
-void rot_q8_tma_plan(int D, int mode, int stages_wanted, int *threads, int *stages, int *stage_bytes, int *gate_offset,
-                     size_t *smem);
 cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, float *sa, int M, int D, int block,
                               int mode, int out_hr, int scale_mode, int stages_wanted, int sms, int *status,
                               cudaStream_t stream);
+// The norm + modulation front end on the same TMA-fed kernel: fp32 rows of up to 8192 channels, no fused residual
+// update. `map` describes x as {32 floats, cols / 32, M} with box {32, D / 32, 1} and 128-byte swizzle.
+bool norm_mod_q8_tma_supported(int D);
+cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const float *mod, long long mod_stride,
+                                   const unsigned char *rtype, void *out, float *sa, int M, int D, int block, float eps,
+                                   int ln, int out_kind, int stages_wanted, int sms, int *status, cudaStream_t stream);
 
 // out[m][n] = c_dtype(float(acc[m][n]) * sa[m] * sw[n] + bias[n]): the product's epilogue applied to accumulators
 // that were summed elsewhere (row-parallel layers reduce their int32 partial accumulators over the GPUs first).

@@ -1,23 +1,27 @@
-// Rotate + per-token int8 quantise, TMA-fed variant for 16-bit inputs (the path's normal case).
+// Rotate + per-token int8 quantise, TMA-fed: the normal case of the path (16-bit activations, rows of up to 16384
+// channels) and the norm + modulation front end on the fp32 residual stream (rows of up to 8192 channels).
 //
-// Same arithmetic as rot_q8.cu (the reference's kernel rot_q8, kernels/ops.metal:274-334, operation by operation);
-// what differs is how rows reach the registers. Rows are fetched by TMA into a ring of shared-memory stages a few
-// rows ahead of the arithmetic, so the kernel has tens of kilobytes per SM in flight without spending registers or
-// load instructions on it, and the warps only compute:
-//   * the input [M][x_stride] is described to TMA as a 3-D tensor {64 channels, cols / 64 chunks, M rows}; one
-//     cp.async.bulk.tensor copy brings a whole row (D / 64 chunks of 128 bytes) into a stage, 128-byte swizzled;
-//   * thread t owns chunk t: it reads its 128 bytes with eight 16-byte shared-memory loads; the swizzle places
-//     piece k of chunk t at column k ^ (t & 7), so the eight threads of a quarter-warp hit eight different bank
-//     groups although their chunks lie 128 bytes apart;
-//   * after the row maximum has been exchanged (the one CTA barrier per row) every thread has finished reading the
-//     stage, and thread 0 re-arms it with the row `stages` rows ahead; no separate "empty" barrier is needed.
-// A CTA has one warp per 2048 channels (D <= 16384); CTAs are persistent over rows m = blockIdx.x, += gridDim.x.
-// Waits on the stage barriers are bounded: on a timeout the CTA sets the context's status word, stops taking rows,
-// waits (bounded) for its copies in flight and returns.
+// Same arithmetic as rot_q8.cu / norm_mod_q8.cu (the reference's kernels rot_q8, kernels/ops.metal:274-334, and
+// norm_mod_q8, :111-268, operation by operation); what differs is how rows reach the registers. Rows are fetched by
+// TMA into a ring of shared-memory stages ahead of the arithmetic, so the kernel has tens of kilobytes per SM in
+// flight without spending registers or load instructions on it, and the warps only compute:
+//   * the input [M][stride] is described to TMA as a 3-D tensor {128 bytes of channels, chunks, M rows}; one
+//     cp.async.bulk.tensor copy brings a whole row into a stage, 128-byte swizzled;
+//   * thread t owns 64 consecutive channels: one 128-byte shared-memory line for 16-bit inputs (eight 16-byte
+//     loads), two lines for fp32. The swizzle places piece k of line r at column k ^ (r & 7), so the eight threads
+//     of a quarter-warp hit different bank groups although their lines lie 128 (or 256) bytes apart;
+//   * after the first CTA barrier of a row (the exchange of the row statistic: the sum of squares with the norm
+//     front end, else the row maximum) every thread has finished reading the stage, and thread 0 re-arms it with
+//     the row `stages` rows ahead; no separate "empty" barrier is needed.
+// One warp per 2048 channels; CTAs are persistent over rows m = blockIdx.x, += gridDim.x. Only one thread polls a
+// stage's barrier; the CTA barrier that follows releases everybody with a uniform go / stop decision. Waits are
+// bounded: on a timeout the CTA sets the context's status word, stops taking rows, waits (bounded) for its copies
+// in flight and returns.
 #include <cuda.h>
 
 #include <map>
 #include <mutex>
+#include <tuple>
 
 #include "kernels.h"
 #include "ptx.cuh"
@@ -29,44 +33,74 @@ namespace {
 using namespace rot;
 
 constexpr int kMaxStages = 4;
+enum Front : int { kPlain = 0, kSwiglu = 1, kNorm = 2 };           // what happens before the rotation
+enum OutKind : int { kOutQ8 = 0, kOutF32 = 1, kOutF16 = 2, kOutHr = 3 };  // codes+scales, modulated fp32 / fp16, rotated fp16
 
 struct RotTmaArgs {
-  CUtensorMap map;     // {64, cols / 64, M} of the 16-bit input, box {64, D / 64, 1}, 128-byte swizzle
+  CUtensorMap map;     // {128 bytes of channels, cols * esize / 128, M}, box {., D * esize / 128, 1}, 128-byte swizzle
   void *out;
   float *sa;
   int *status;
+  const float *mod;            // norm front end: per row type D scale' then D shift values
+  const unsigned char *rtype;  // norm front end: row types
+  long long mod_stride;
   int M, D;
   int stages;          // ring depth
   int stage_bytes;     // bytes per stage (value row, then gate row; each padded to 1024)
   int gate_offset;     // offset of the gate row inside a stage
   float normaliser;
+  float eps;
   int scale_mode;      // 0: scale from this row's maximum; 1: only write the maximum to sa; 2: sa holds the maximum to use
 };
 
-// 64 consecutive 16-bit values of chunk `t` of a stage, widened to fp32.
-template <bool IS_HALF>
+// 64 consecutive values of the thread's chunk `t`, widened to fp32. IN: 0 bf16, 1 fp16 (one line), 2 fp32 (two lines).
+template <int IN>
 __device__ __forceinline__ void read_chunk(const uint8_t *stage, int t, float (&v)[kChunk]) {
-  const uint8_t *row = stage + t * 128;
-  const int sw = t & 7;
+  if constexpr (IN == 2) {
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const uint4 q = *reinterpret_cast<const uint4 *>(row + ((k ^ sw) << 4));
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    for (int half = 0; half < 2; ++half) {
+      const int line = 2 * t + half;
+      const uint8_t *row = stage + line * 128;
+      const int sw = line & 7;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (IS_HALF) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
-        v[8 * k + 2 * j] = f.x;
-        v[8 * k + 2 * j + 1] = f.y;
-      } else {
-        v[8 * k + 2 * j] = __uint_as_float(w[j] << 16);
-        v[8 * k + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+      for (int k = 0; k < 8; ++k) {
+        const float4 q = *reinterpret_cast<const float4 *>(row + ((k ^ sw) << 4));
+        v[32 * half + 4 * k] = q.x; v[32 * half + 4 * k + 1] = q.y;
+        v[32 * half + 4 * k + 2] = q.z; v[32 * half + 4 * k + 3] = q.w;
+      }
+    }
+  } else {
+    const uint8_t *row = stage + t * 128;
+    const int sw = t & 7;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint4 q = *reinterpret_cast<const uint4 *>(row + ((k ^ sw) << 4));
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (IN == 1) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
+          v[8 * k + 2 * j] = f.x;
+          v[8 * k + 2 * j + 1] = f.y;
+        } else {
+          v[8 * k + 2 * j] = __uint_as_float(w[j] << 16);
+          v[8 * k + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+        }
       }
     }
   }
 }
 
-template <bool IS_HALF, int BLOCK, bool SWIGLU, bool OUT_HR>
+// Sum of the thread's 64 values: four interleaved partial sums, combined pairwise. With the lane tree and the
+// sequential pass over the warps below this fixes the (fp32) summation order of the row statistics.
+__device__ __forceinline__ float sum64(const float (&v)[kChunk], bool squares) {
+  float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int i = 0; i < kChunk; ++i) s[i & 3] = __fadd_rn(s[i & 3], squares ? __fmul_rn(v[i], v[i]) : v[i]);
+  return __fadd_rn(__fadd_rn(s[0], s[1]), __fadd_rn(s[2], s[3]));
+}
+
+template <int IN, int BLOCK, int FRONT, bool LN, int OUT>
 __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__ RotTmaArgs p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -74,21 +108,23 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
   uint8_t *base_ptr = smem_raw + (base - raw_addr);
   const uint32_t tail = p.stages * p.stage_bytes;
   const uint32_t bars = base + tail;                                       // full[kMaxStages]
-  float *warp_max = reinterpret_cast<float *>(base_ptr + tail + 64);       // [2][8]
-  volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + tail + 128);
+  float *exchange = reinterpret_cast<float *>(base_ptr + tail + 64);       // [4][8]: row statistics, rotating buffers
+  volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + tail + 192);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n_warps = blockDim.x >> 5;
   const int n_chunks = p.D / kChunk;
   const bool active = tid < n_chunks;
   const float2 norm2 = make_float2(p.normaliser, p.normaliser);
-  const uint32_t row_bytes = static_cast<uint32_t>(p.D) * 2u;
+  constexpr int kEsize = IN == 2 ? 4 : 2;
+  const uint32_t row_bytes = static_cast<uint32_t>(p.D) * kEsize;
+  const int lines = p.D * kEsize / 128;  // 128-byte lines per row
 
   auto issue = [&](int s, int m) {  // thread 0 only
     const uint32_t bar = bars + 8u * s;
-    mbar_arrive_expect_tx(bar, SWIGLU ? 2u * row_bytes : row_bytes);
+    mbar_arrive_expect_tx(bar, FRONT == kSwiglu ? 2u * row_bytes : row_bytes);
     tma_load_3d(base + s * p.stage_bytes, &p.map, bar, 0, 0, m);
-    if (SWIGLU) tma_load_3d(base + s * p.stage_bytes + p.gate_offset, &p.map, bar, 0, n_chunks, m);
+    if (FRONT == kSwiglu) tma_load_3d(base + s * p.stage_bytes + p.gate_offset, &p.map, bar, 0, lines, m);
   };
 
   if (tid == 0) {
@@ -106,21 +142,35 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
   }
 
   int it = 0;
+  unsigned xbuf = 0;  // which exchange buffer the next CTA-wide reduction uses
+  // CTA-wide reduction of one value per thread: lane tree, then the warps in order. One barrier per call.
+  auto cta_reduce = [&](float v, bool is_max) {
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) {
+      const float o = __shfl_xor_sync(0xFFFFFFFFu, v, sft);
+      v = is_max ? fmaxf(v, o) : __fadd_rn(v, o);
+    }
+    float *buf = exchange + (xbuf++ & 3u) * 8;
+    if (lane == 0) buf[warp] = v;
+    __syncthreads();
+    float r = buf[0];
+    for (int w = 1; w < n_warps; ++w) r = is_max ? fmaxf(r, buf[w]) : __fadd_rn(r, buf[w]);
+    return r;
+  };
+
   for (int m = blockIdx.x; m < p.M; m += gridDim.x, ++it) {
     const int s = it % p.stages;
     const uint32_t ph = (it / p.stages) & 1u;
-    // One thread polls the stage's barrier (a whole CTA spinning on it would eat the issue slots the arithmetic
-    // needs); the CTA barrier then releases everybody with a uniform decision: all threads go on or none does.
     const bool arrived = tid != 0 || mbar_wait(bars + 8u * s, ph, cta_abort, p.status, kStatusRotTimeout);
     if (!__syncthreads_and(arrived)) break;
 
     const uint8_t *stage = base_ptr + s * p.stage_bytes;
     float v[kChunk];
     if (active) {
-      read_chunk<IS_HALF>(stage, tid, v);
-      if (SWIGLU) {
+      read_chunk<IN>(stage, tid, v);
+      if (FRONT == kSwiglu) {
         float g[kChunk];
-        read_chunk<IS_HALF>(stage + p.gate_offset, tid, g);
+        read_chunk<IN>(stage + p.gate_offset, tid, g);
 #pragma unroll
         for (int i = 0; i < kChunk; ++i) v[i] = __fmul_rn(v[i], silu(g[i]));
       }
@@ -128,33 +178,66 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
 #pragma unroll
       for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
     }
-    chunk_butterflies(v);
-    lane_butterflies<BLOCK>(v, lane);
-    float amax = 0.0f;
+    bool refilled = false;
+    auto refill = [&]() {  // after a CTA barrier that follows the reads: the stage may be overwritten
+      if (!refilled && tid == 0) {
+        const int m_next = m + p.stages * static_cast<int>(gridDim.x);
+        if (m_next < p.M) issue(s, m_next);
+      }
+      refilled = true;
+    };
+
+    if constexpr (FRONT == kNorm) {
+      // RMSNorm (LayerNorm: mean removed first), then v * inv * scale'[type] + shift[type]
+      const float fd = static_cast<float>(p.D);
+      if (LN) {
+        const float mean = __fdiv_rn(cta_reduce(sum64(v, false), false), fd);
+        refill();
+        if (active) {
 #pragma unroll
-    for (int i = 0; i < kChunk; i += 2) {
-      const float2 r = __fmul2_rn(make_float2(v[i], v[i + 1]), norm2);
-      v[i] = r.x; v[i + 1] = r.y;
-      amax = fmaxf(amax, fmaxf(fabsf(r.x), fabsf(r.y)));
-    }
+          for (int i = 0; i < kChunk; ++i) v[i] = __fsub_rn(v[i], mean);
+        }
+      }
+      const float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(cta_reduce(sum64(v, true), false), fd), p.eps));
+      refill();
+      if (active) {
+        const float *md = p.mod + static_cast<size_t>(p.rtype[m]) * p.mod_stride + tid * kChunk;
+        const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-    for (int sft = 16; sft > 0; sft >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, sft));
-    float *wm = warp_max + (it & 1) * 8;
-    if (lane == 0) wm[warp] = amax;
-    __syncthreads();  // row maximum exchanged; also: every thread is done reading this stage
-    if (tid == 0) {
-      const int m_next = m + p.stages * static_cast<int>(gridDim.x);
-      if (m_next < p.M) issue(s, m_next);
+        for (int q = 0; q < kChunk / 4; ++q) {
+          const float4 s4 = __ldg(reinterpret_cast<const float4 *>(md) + q);
+          const float4 b4 = __ldg(reinterpret_cast<const float4 *>(md + p.D) + q);
+          float2 x0 = __fmul2_rn(__fmul2_rn(make_float2(v[4 * q], v[4 * q + 1]), inv2), make_float2(s4.x, s4.y));
+          float2 x1 = __fmul2_rn(__fmul2_rn(make_float2(v[4 * q + 2], v[4 * q + 3]), inv2), make_float2(s4.z, s4.w));
+          x0 = __fadd2_rn(x0, make_float2(b4.x, b4.y));
+          x1 = __fadd2_rn(x1, make_float2(b4.z, b4.w));
+          v[4 * q] = x0.x; v[4 * q + 1] = x0.y; v[4 * q + 2] = x1.x; v[4 * q + 3] = x1.y;
+        }
+      }
     }
-    float row_max = wm[0];
-    for (int w = 1; w < n_warps; ++w) row_max = fmaxf(row_max, wm[w]);
-    if (!OUT_HR && p.scale_mode == 1) {  // a shard of a longer row: hand the local maximum to the caller
-      if (tid == 0) p.sa[m] = row_max;
+
+    if constexpr (OUT == kOutF32) {
+      if (active) {
+        float4 *o = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + static_cast<size_t>(m) * p.D + tid * kChunk);
+#pragma unroll
+        for (int q = 0; q < kChunk / 4; ++q) o[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      }
       continue;
     }
-    if (!OUT_HR && p.scale_mode == 2) row_max = p.sa[m];  // the whole row's maximum, reduced over the shards
-
-    if constexpr (OUT_HR) {
+    if constexpr (OUT != kOutF16) {  // rotation
+      chunk_butterflies(v);
+      lane_butterflies<BLOCK>(v, lane);
+#pragma unroll
+      for (int i = 0; i < kChunk; i += 2) {
+        const float2 r = __fmul2_rn(make_float2(v[i], v[i + 1]), norm2);
+        v[i] = r.x; v[i + 1] = r.y;
+      }
+    }
+    if constexpr (OUT == kOutF16 || OUT == kOutHr) {
+      if (FRONT != kNorm) {  // no statistic was exchanged: a barrier of its own frees the stage
+        __syncthreads();
+        refill();
+      }
       if (active) {
         __half *dst = static_cast<__half *>(p.out) + static_cast<size_t>(m) * p.D + tid * kChunk;
 #pragma unroll
@@ -168,7 +251,19 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
           reinterpret_cast<uint4 *>(dst)[q] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
-    } else {
+      continue;
+    }
+    if constexpr (OUT == kOutQ8) {
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < kChunk; i += 2) amax = fmaxf(amax, fmaxf(fabsf(v[i]), fabsf(v[i + 1])));
+      float row_max = cta_reduce(amax, true);
+      refill();
+      if (p.scale_mode == 1) {  // a shard of a longer row: hand the local maximum to the caller
+        if (tid == 0) p.sa[m] = row_max;
+        continue;
+      }
+      if (p.scale_mode == 2) row_max = p.sa[m];  // the whole row's maximum, reduced over the shards
       const float scale = row_max > 0.0f ? __fdiv_rn(row_max, 127.0f) : 1.0f;
       const float rs = __fdiv_rn(1.0f, scale);
       const float2 rs2 = make_float2(rs, rs);
@@ -214,33 +309,47 @@ int resident_ctas(const void *fn, int threads, size_t smem) {
   return n;
 }
 
-template <bool IS_HALF, int BLOCK, bool SWIGLU, bool OUT_HR>
+template <int IN, int BLOCK, int FRONT, bool LN, int OUT>
 cudaError_t launch_final(const RotTmaArgs &a, int threads, size_t smem, int sms, cudaStream_t stream) {
-  auto *fn = rot_q8_tma_kernel<IS_HALF, BLOCK, SWIGLU, OUT_HR>;
+  auto *fn = rot_q8_tma_kernel<IN, BLOCK, FRONT, LN, OUT>;
   const long long resident = static_cast<long long>(sms) * resident_ctas(reinterpret_cast<const void *>(fn), threads, smem);
   const int grid = static_cast<int>(a.M < resident ? a.M : resident);
   fn<<<grid, threads, smem, stream>>>(a);
   return cudaGetLastError();
 }
 
-template <bool IS_HALF, int BLOCK>
-cudaError_t launch_mode(const RotTmaArgs &a, int threads, size_t smem, int sms, int mode, int out_hr, cudaStream_t stream) {
+template <int IN, int BLOCK>
+cudaError_t launch_rot(const RotTmaArgs &a, int threads, size_t smem, int sms, int mode, int out_hr, cudaStream_t stream) {
   if (out_hr) {
-    return mode == 1 ? launch_final<IS_HALF, BLOCK, true, true>(a, threads, smem, sms, stream)
-                     : launch_final<IS_HALF, BLOCK, false, true>(a, threads, smem, sms, stream);
+    return mode == 1 ? launch_final<IN, BLOCK, kSwiglu, false, kOutHr>(a, threads, smem, sms, stream)
+                     : launch_final<IN, BLOCK, kPlain, false, kOutHr>(a, threads, smem, sms, stream);
   }
-  return mode == 1 ? launch_final<IS_HALF, BLOCK, true, false>(a, threads, smem, sms, stream)
-                   : launch_final<IS_HALF, BLOCK, false, false>(a, threads, smem, sms, stream);
+  return mode == 1 ? launch_final<IN, BLOCK, kSwiglu, false, kOutQ8>(a, threads, smem, sms, stream)
+                   : launch_final<IN, BLOCK, kPlain, false, kOutQ8>(a, threads, smem, sms, stream);
 }
 
-template <bool IS_HALF>
-cudaError_t launch_block(const RotTmaArgs &a, int block, int threads, size_t smem, int sms, int mode, int out_hr,
-                         cudaStream_t stream) {
-  switch (block) {
-    case 64: return launch_mode<IS_HALF, 64>(a, threads, smem, sms, mode, out_hr, stream);
-    case 128: return launch_mode<IS_HALF, 128>(a, threads, smem, sms, mode, out_hr, stream);
-    default: return launch_mode<IS_HALF, 256>(a, threads, smem, sms, mode, out_hr, stream);
+template <int BLOCK, bool LN>
+cudaError_t launch_norm(const RotTmaArgs &a, int threads, size_t smem, int sms, int out_kind, cudaStream_t stream) {
+  switch (out_kind) {
+    case kOutQ8: return launch_final<2, BLOCK, kNorm, LN, kOutQ8>(a, threads, smem, sms, stream);
+    case kOutF32: return launch_final<2, BLOCK, kNorm, LN, kOutF32>(a, threads, smem, sms, stream);
+    case kOutF16: return launch_final<2, BLOCK, kNorm, LN, kOutF16>(a, threads, smem, sms, stream);
+    default: return launch_final<2, BLOCK, kNorm, LN, kOutHr>(a, threads, smem, sms, stream);
   }
+}
+
+void plan(int D, int esize, bool gates, int stages_wanted, RotTmaArgs *a, int *threads, size_t *smem) {
+  const int row = (D * esize + 1023) / 1024 * 1024;
+  a->gate_offset = row;
+  a->stage_bytes = gates ? 2 * row : row;
+  // measured: one row ahead (2 stages) is best for plain rows; with gates a stage is twice as large and a single
+  // stage, which lets more CTAs share an SM, wins
+  int s = stages_wanted > 0 ? stages_wanted : (gates ? 1 : 2);
+  if (s > kMaxStages) s = kMaxStages;
+  while (s > 1 && static_cast<size_t>(s) * a->stage_bytes + 2048 > 232448) --s;
+  a->stages = s;
+  *threads = (D / kChunk + 31) / 32 * 32;
+  *smem = 1024 + static_cast<size_t>(s) * a->stage_bytes + 256;
 }
 
 }  // namespace
@@ -248,34 +357,45 @@ cudaError_t launch_block(const RotTmaArgs &a, int block, int threads, size_t sme
 bool rot_q8_tma_supported(int x_dtype, int D) {
   return (x_dtype == kDtypeBf16 || x_dtype == kDtypeF16) && D % kChunk == 0 && D / kChunk <= 256;
 }
-
-void rot_q8_tma_plan(int D, int mode, int stages_wanted, int *threads, int *stages, int *stage_bytes, int *gate_offset,
-                     size_t *smem) {
-  const int row = (D * 2 + 1023) / 1024 * 1024;
-  *gate_offset = row;
-  *stage_bytes = mode == 1 ? 2 * row : row;
-  // measured: one row ahead (2 stages) is best for plain rows; with gates a stage is twice as large and a single
-  // stage, which lets more CTAs share an SM, wins
-  int s = stages_wanted > 0 ? stages_wanted : (mode == 1 ? 1 : 2);
-  if (s > kMaxStages) s = kMaxStages;
-  while (s > 1 && static_cast<size_t>(s) * *stage_bytes + 2048 > 232448) --s;
-  *stages = s;
-  *threads = (D / kChunk + 31) / 32 * 32;
-  *smem = 1024 + static_cast<size_t>(s) * *stage_bytes + 256;
-}
+bool norm_mod_q8_tma_supported(int D) { return D % kChunk == 0 && D / 32 <= 256; }  // the box holds D / 32 lines
 
 cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, float *sa, int M, int D, int block,
                               int mode, int out_hr, int scale_mode, int stages_wanted, int sms, int *status,
                               cudaStream_t stream) {
-  RotTmaArgs a;
+  RotTmaArgs a = {};
   a.map = map; a.out = out; a.sa = sa; a.status = status; a.M = M; a.D = D; a.scale_mode = scale_mode;
   a.normaliser = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
   int threads;
   size_t smem;
-  rot_q8_tma_plan(D, mode, stages_wanted, &threads, &a.stages, &a.stage_bytes, &a.gate_offset, &smem);
+  plan(D, 2, mode == 1, stages_wanted, &a, &threads, &smem);
   if (threads > 256 || smem > 232448) return cudaErrorInvalidConfiguration;
-  return x_dtype == kDtypeF16 ? launch_block<true>(a, block, threads, smem, sms, mode, out_hr, stream)
-                              : launch_block<false>(a, block, threads, smem, sms, mode, out_hr, stream);
+#define H3B_ROT(IN)                                                                    \
+  switch (block) {                                                                     \
+    case 64: return launch_rot<IN, 64>(a, threads, smem, sms, mode, out_hr, stream);   \
+    case 128: return launch_rot<IN, 128>(a, threads, smem, sms, mode, out_hr, stream); \
+    default: return launch_rot<IN, 256>(a, threads, smem, sms, mode, out_hr, stream);  \
+  }
+  if (x_dtype == kDtypeF16) { H3B_ROT(1) }
+  H3B_ROT(0)
+#undef H3B_ROT
+}
+
+cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const float *mod, long long mod_stride,
+                                   const unsigned char *rtype, void *out, float *sa, int M, int D, int block, float eps,
+                                   int ln, int out_kind, int stages_wanted, int sms, int *status, cudaStream_t stream) {
+  RotTmaArgs a = {};
+  a.map = map; a.out = out; a.sa = sa; a.status = status; a.M = M; a.D = D; a.scale_mode = 0;
+  a.mod = mod; a.mod_stride = mod_stride; a.rtype = rtype; a.eps = eps;
+  a.normaliser = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
+  int threads;
+  size_t smem;
+  plan(D, 4, false, stages_wanted, &a, &threads, &smem);
+  if (threads > 256 || smem > 232448) return cudaErrorInvalidConfiguration;
+  switch (block) {
+    case 64: return ln ? launch_norm<64, true>(a, threads, smem, sms, out_kind, stream) : launch_norm<64, false>(a, threads, smem, sms, out_kind, stream);
+    case 128: return ln ? launch_norm<128, true>(a, threads, smem, sms, out_kind, stream) : launch_norm<128, false>(a, threads, smem, sms, out_kind, stream);
+    default: return ln ? launch_norm<256, true>(a, threads, smem, sms, out_kind, stream) : launch_norm<256, false>(a, threads, smem, sms, out_kind, stream);
+  }
 }
 
 }  // namespace h3b
