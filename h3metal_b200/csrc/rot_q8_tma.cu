@@ -342,9 +342,9 @@ void plan(int D, int esize, bool gates, int stages_wanted, RotTmaArgs *a, int *t
   const int row = (D * esize + 1023) / 1024 * 1024;
   a->gate_offset = row;
   a->stage_bytes = gates ? 2 * row : row;
-  // measured: one row ahead (2 stages) is best for plain rows; with gates a stage is twice as large and a single
-  // stage, which lets more CTAs share an SM, wins
-  int s = stages_wanted > 0 ? stages_wanted : (gates ? 1 : 2);
+  // measured: one row ahead (2 stages) is best for plain 16-bit rows; with gates, or with fp32 rows, a stage is
+  // twice as large and a single stage, which lets more CTAs share an SM, wins
+  int s = stages_wanted > 0 ? stages_wanted : ((gates || esize == 4) ? 1 : 2);
   if (s > kMaxStages) s = kMaxStages;
   while (s > 1 && static_cast<size_t>(s) * a->stage_bytes + 2048 > 232448) --s;
   a->stages = s;
