@@ -347,13 +347,18 @@ int h3b_norm_mod_q8(h3b_ctx *ctx, float *x, int64_t x_stride, const float *mod, 
       (y && reinterpret_cast<uintptr_t>(y) % 16) || (post && reinterpret_cast<uintptr_t>(post) % 16))
     return fail("norm_mod_q8: tensors must be 16-byte aligned with row strides that are multiples of 16 bytes");
   cudaEvent_t ps = nullptr;
-  if (!post && ctx->rot_stages >= 0 && h3b::norm_mod_q8_tma_supported(D)) {
+  if (!post && ctx->rot_stages >= 0 && h3b::norm_mod_q8_tma_supported(D) && mod_stride % 32 == 0) {
     // rows reach shared memory by TMA: x seen as {32 floats, x_stride / 32 lines, M rows}
     const CUtensorMap *map = ctx->tensor_map3(x, h3b::kDtypeF32, 32, static_cast<uint64_t>(D) / 32, M, 128,
                                               static_cast<uint64_t>(x_stride) * 4, 32, static_cast<uint32_t>(D / 32), 128);
     if (!map) return -1;
+    const CUtensorMap map_x = *map;  // the cache may move when the second descriptor is inserted
+    // the modulation table seen the same way: {32 floats, mod_stride / 32 lines, up to 256 row types}
+    const CUtensorMap *mmap = ctx->tensor_map3(mod, h3b::kDtypeF32, 32, static_cast<uint64_t>(mod_stride) / 32, 256, 128,
+                                               static_cast<uint64_t>(mod_stride) * 4, 32, static_cast<uint32_t>(D / 32), 128);
+    if (!mmap) return -1;
     if (ctx->before_launch(&ps)) return -1;
-    const cudaError_t e = h3b::launch_norm_mod_q8_tma(*map, mod, mod_stride, rtype, out, sa, M, D, block, eps, ln, out_kind,
+    const cudaError_t e = h3b::launch_norm_mod_q8_tma(map_x, *mmap, mod, mod_stride, rtype, out, sa, M, D, block, eps, ln, out_kind,
                                                       ctx->rot_stages, ctx->prop.multiProcessorCount, ctx->status_dev,
                                                       ctx->stream);
     return ctx->after_launch("norm_mod_q8 launch", e);

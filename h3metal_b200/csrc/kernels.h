@@ -28,11 +28,13 @@ cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, fl
                               int mode, int out_hr, int scale_mode, int stages_wanted, int sms, int *status,
                               cudaStream_t stream);
 // The norm + modulation front end on the same TMA-fed kernel: fp32 rows of up to 8192 channels, no fused residual
-// update. `map` describes x as {32 floats, cols / 32, M} with box {32, D / 32, 1} and 128-byte swizzle.
+// update. `map` describes x as {32 floats, D / 32, M} and `map_mod` the modulation table as
+// {32 floats, mod_stride / 32, types}, both with box {32, D / 32, 1} and 128-byte swizzle.
 bool norm_mod_q8_tma_supported(int D);
-cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const float *mod, long long mod_stride,
-                                   const unsigned char *rtype, void *out, float *sa, int M, int D, int block, float eps,
-                                   int ln, int out_kind, int stages_wanted, int sms, int *status, cudaStream_t stream);
+cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const CUtensorMap &map_mod, const float *mod,
+                                   long long mod_stride, const unsigned char *rtype, void *out, float *sa, int M, int D,
+                                   int block, float eps, int ln, int out_kind, int stages_wanted, int sms, int *status,
+                                   cudaStream_t stream);
 
 // out[m][n] = c_dtype(float(acc[m][n]) * sa[m] * sw[n] + bias[n]): the product's epilogue applied to accumulators
 // that were summed elsewhere (row-parallel layers reduce their int32 partial accumulators over the GPUs first).

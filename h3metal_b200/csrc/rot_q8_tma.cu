@@ -38,6 +38,7 @@ enum OutKind : int { kOutQ8 = 0, kOutF32 = 1, kOutF16 = 2, kOutHr = 3 };  // cod
 
 struct RotTmaArgs {
   CUtensorMap map;     // {128 bytes of channels, cols * esize / 128, M}, box {., D * esize / 128, 1}, 128-byte swizzle
+  CUtensorMap map_mod; // norm front end: the modulation table as {32 floats, mod_stride / 32, types}, same box
   void *out;
   float *sa;
   int *status;
@@ -47,7 +48,7 @@ struct RotTmaArgs {
   int M, D;
   int stages;          // ring depth
   int stage_bytes;     // bytes per stage (value row, then gate row; each padded to 1024)
-  int gate_offset;     // offset of the gate row inside a stage
+  int gate_offset;     // offset of the gate row (or, norm front end, of the scale' row; the shift row follows) in a stage
   float normaliser;
   float eps;
   int scale_mode;      // 0: scale from this row's maximum; 1: only write the maximum to sa; 2: sa holds the maximum to use
@@ -122,13 +123,21 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
 
   auto issue = [&](int s, int m) {  // thread 0 only
     const uint32_t bar = bars + 8u * s;
-    mbar_arrive_expect_tx(bar, FRONT == kSwiglu ? 2u * row_bytes : row_bytes);
+    mbar_arrive_expect_tx(bar, FRONT == kPlain ? row_bytes : FRONT == kSwiglu ? 2u * row_bytes : 3u * row_bytes);
     tma_load_3d(base + s * p.stage_bytes, &p.map, bar, 0, 0, m);
     if (FRONT == kSwiglu) tma_load_3d(base + s * p.stage_bytes + p.gate_offset, &p.map, bar, 0, lines, m);
+    if (FRONT == kNorm) {
+      // the row's scale' and shift vectors ride along (from L2, where the small table lives), so that the
+      // modulation reads shared memory instead of waiting on dependent global loads
+      const int type = p.rtype[m];
+      tma_load_3d(base + s * p.stage_bytes + p.gate_offset, &p.map_mod, bar, 0, 0, type);
+      tma_load_3d(base + s * p.stage_bytes + 2 * p.gate_offset, &p.map_mod, bar, 0, lines, type);
+    }
   };
 
   if (tid == 0) {
     tma_prefetch_descriptor(&p.map);
+    if (FRONT == kNorm) tma_prefetch_descriptor(&p.map_mod);
     for (int s = 0; s < p.stages; ++s) mbar_init(bars + 8u * s, 1);
     *cta_abort = 0;
     fence_barrier_init();
@@ -192,27 +201,27 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
       const float fd = static_cast<float>(p.D);
       if (LN) {
         const float mean = __fdiv_rn(cta_reduce(sum64(v, false), false), fd);
-        refill();
         if (active) {
 #pragma unroll
           for (int i = 0; i < kChunk; ++i) v[i] = __fsub_rn(v[i], mean);
         }
       }
       const float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(cta_reduce(sum64(v, true), false), fd), p.eps));
-      refill();
       if (active) {
-        const float *md = p.mod + static_cast<size_t>(p.rtype[m]) * p.mod_stride + tid * kChunk;
+        float sc[kChunk], sh[kChunk];
+        read_chunk<2>(stage + p.gate_offset, tid, sc);
+        read_chunk<2>(stage + 2 * p.gate_offset, tid, sh);
         const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-        for (int q = 0; q < kChunk / 4; ++q) {
-          const float4 s4 = __ldg(reinterpret_cast<const float4 *>(md) + q);
-          const float4 b4 = __ldg(reinterpret_cast<const float4 *>(md + p.D) + q);
-          float2 x0 = __fmul2_rn(__fmul2_rn(make_float2(v[4 * q], v[4 * q + 1]), inv2), make_float2(s4.x, s4.y));
-          float2 x1 = __fmul2_rn(__fmul2_rn(make_float2(v[4 * q + 2], v[4 * q + 3]), inv2), make_float2(s4.z, s4.w));
-          x0 = __fadd2_rn(x0, make_float2(b4.x, b4.y));
-          x1 = __fadd2_rn(x1, make_float2(b4.z, b4.w));
-          v[4 * q] = x0.x; v[4 * q + 1] = x0.y; v[4 * q + 2] = x1.x; v[4 * q + 3] = x1.y;
+        for (int i = 0; i < kChunk; i += 2) {
+          float2 x = __fmul2_rn(__fmul2_rn(make_float2(v[i], v[i + 1]), inv2), make_float2(sc[i], sc[i + 1]));
+          x = __fadd2_rn(x, make_float2(sh[i], sh[i + 1]));
+          v[i] = x.x; v[i + 1] = x.y;
         }
+      }
+      if (OUT == kOutF32 || OUT == kOutF16) {  // no further exchange follows: free the stage with a barrier of its own
+        __syncthreads();
+        refill();
       }
     }
 
@@ -234,7 +243,7 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
       }
     }
     if constexpr (OUT == kOutF16 || OUT == kOutHr) {
-      if (FRONT != kNorm) {  // no statistic was exchanged: a barrier of its own frees the stage
+      if (!(FRONT == kNorm && OUT == kOutF16)) {  // no exchange follows the last read: a barrier of its own frees the stage
         __syncthreads();
         refill();
       }
@@ -341,7 +350,7 @@ cudaError_t launch_norm(const RotTmaArgs &a, int threads, size_t smem, int sms, 
 void plan(int D, int esize, bool gates, int stages_wanted, RotTmaArgs *a, int *threads, size_t *smem) {
   const int row = (D * esize + 1023) / 1024 * 1024;
   a->gate_offset = row;
-  a->stage_bytes = gates ? 2 * row : row;
+  a->stage_bytes = esize == 4 ? 3 * row : gates ? 2 * row : row;  // fp32 rows carry their scale' and shift vectors
   // measured: one row ahead (2 stages) is best for plain 16-bit rows; with gates, or with fp32 rows, a stage is
   // twice as large and a single stage, which lets more CTAs share an SM, wins
   int s = stages_wanted > 0 ? stages_wanted : ((gates || esize == 4) ? 1 : 2);
@@ -380,11 +389,12 @@ cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, fl
 #undef H3B_ROT
 }
 
-cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const float *mod, long long mod_stride,
-                                   const unsigned char *rtype, void *out, float *sa, int M, int D, int block, float eps,
-                                   int ln, int out_kind, int stages_wanted, int sms, int *status, cudaStream_t stream) {
+cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const CUtensorMap &map_mod, const float *mod,
+                                   long long mod_stride, const unsigned char *rtype, void *out, float *sa, int M, int D,
+                                   int block, float eps, int ln, int out_kind, int stages_wanted, int sms, int *status,
+                                   cudaStream_t stream) {
   RotTmaArgs a = {};
-  a.map = map; a.out = out; a.sa = sa; a.status = status; a.M = M; a.D = D; a.scale_mode = 0;
+  a.map = map; a.map_mod = map_mod; a.out = out; a.sa = sa; a.status = status; a.M = M; a.D = D; a.scale_mode = 0;
   a.mod = mod; a.mod_stride = mod_stride; a.rtype = rtype; a.eps = eps;
   a.normaliser = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
   int threads;
