@@ -124,6 +124,33 @@ def main():
         out[f"norm_{tag}_expect_y_f64"] = yy
         out[f"norm_{tag}_expect_rot_f64"] = ref_test_ops.rot(yy)
 
+    # -- h3metal/weights.py: a small .h3m file written by the reference's Writer (stored gzipped: 8 MiB of it are the
+    #    reserved, zero-filled header region) ------------------------------------------------------------------------
+    import gzip
+    import tempfile
+    from h3metal.weights import Writer
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "t.h3m")
+        wr = Writer(path, {"kind": "test", "hidden": 512})
+        wr.tensor("a", np.arange(1000, dtype=np.float32), "f32")
+        wr.tensor("cpu_only", np.arange(7, dtype=np.int32), "i32", host_only=True)
+        wr.linear("lin", "q8", 24, 512, out["q8_codes"], out["q8_scales"], bias=np.linspace(-1, 1, 24).astype(np.float32))
+        wr.close()
+        with open(path, "rb") as src, gzip.open(os.path.join(HERE, "ref_file.h3m.gz"), "wb", compresslevel=9) as dst:
+            dst.write(src.read())
+
+    # -- h3metal/lora.py:291-310: A scaled and rotated with the layer's signs, ranks stacked side by side -----------------
+    from h3metal import lora as ref_lora
+    r3 = np.random.default_rng(21)
+    A1, B1 = r3.standard_normal((4, 512)).astype(np.float32), r3.standard_normal((96, 4)).astype(np.float32)
+    A2, B2 = r3.standard_normal((8, 512)).astype(np.float32), r3.standard_normal((96, 8)).astype(np.float32)
+    sgn = out["signs_512_seed3"]
+    t1 = ref_lora.Term(ref_quant.rotate_in((A1 * np.float32(0.8 * 2.0)).astype(np.float32), sgn), B1)
+    t2 = ref_lora.Term(ref_quant.rotate_in((A2 * np.float32(1.0 * 0.5)).astype(np.float32), sgn), B2)
+    sa_, sb_ = ref_lora.stack([t1, t2])
+    out["lora_A1"], out["lora_B1"], out["lora_A2"], out["lora_B2"] = A1, B1, A2, B2
+    out["lora_stack_A"], out["lora_stack_B"] = sa_, sb_
+
     np.savez_compressed(os.path.join(HERE, "ref_golden.npz"), **out)
     print("wrote", len(out), "arrays,", os.path.getsize(os.path.join(HERE, "ref_golden.npz")), "bytes;",
           len(dispatch), "dispatches")

@@ -36,3 +36,45 @@ def test_host_step_equals_device_step(gpu, lora):
         if h is not None:
             assert torch.equal(h.view(torch.int16), w.cpu().view(torch.int16))
     assert blk.launches_per_step == (12 if lora else 8)
+
+
+def test_linear_from_an_h3m_file_with_an_adapter(gpu, tmp_path):
+    """A converted layer read from an .h3m file (weights.WeightFile.linear) with a stacked two-adapter LoRA term
+    (lora.term / order / stack -> ops.low_rank) gives what the oracle computes from the same arrays."""
+    import oracle
+    from oracle import gemm_ref
+    from h3metal_b200 import lora, ops, quant, weights
+    rng = np.random.default_rng(12)
+    M, K, N, block = 256, 1024, 768, 128
+    signs = quant.random_signs(K, 5)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    codes, scales = quant.quantize("q8", quant.rotate_in(w, signs, block))
+    bias = workloads.bias_np(rng, N)
+    path = str(tmp_path / "layer.h3m")
+    wr = weights.Writer(path, {"block": block})
+    wr.linear("blk.0.out", "q8", N, K, codes, scales, bias=bias)
+    wr.close()
+    wf = weights.WeightFile(gpu, path)
+    wt = wf.linear("blk.0.out")
+    terms = [lora.term(rng.standard_normal((8, K)).astype(np.float32) * 0.05, rng.standard_normal((N, 8)).astype(np.float32) * 0.05,
+                       strength=0.7, scale=2.0, signs=signs, block=block) for _ in range(2)]
+    A, B = lora.stack(lora.order(terms))
+    wt.low = ops.low_rank(gpu, A, B, ops.Scratch(gpu))
+    xh = workloads.activations_np(rng, M, K, 4)
+    a8, sa, out = gpu.empty((M, K), "i8"), gpu.empty((M,), "f32"), gpu.empty((M, N), "bf16")
+    # activations go through the same signs before the block rotation: fold them into the input here
+    x_signed = quant.bf16_bits(quant.bf16_to_f32(xh) * signs[None, :])
+    ops.rot_q8(gpu, gpu.upload(x_signed, "bf16"), a8, sa, M, K, block=block)
+    ops.gemm(gpu, a8, wt, out, M, sa=sa, tile=(128, 128, 4))
+    gpu.wait()
+    q, s = oracle.rot_q8_rows(x_signed, K, block=block)
+    assert np.array_equal(a8.numpy(), q) and np.array_equal(sa.numpy(), s)
+    stored, v, _ = gemm_ref.gemm_q8(q, codes, s, scales, bias, gemm_ref.low_rank_ref(A, B), "bf16")
+    got = oracle.bf16_bits_to_f32(out.numpy()).astype(np.float64)
+    assert np.linalg.norm(got - oracle.bf16_bits_to_f32(stored)) / np.linalg.norm(v) <= 1e-3
+    # and the quantised layer still approximates the float layer with its adapters (int8 error level)
+    dense = quant.bf16_to_f32(xh).astype(np.float64) @ w.T.astype(np.float64) + bias
+    for t in terms:
+        dense += quant.rotate_in(quant.bf16_to_f32(xh) * 1.0, signs, block).astype(np.float64) @ t.A.T.astype(np.float64) @ t.B.T.astype(np.float64)
+    assert np.linalg.norm(got - dense) / np.linalg.norm(dense) < 0.03
+    wf.close()
