@@ -1,6 +1,7 @@
 """Generates tests/golden/ref_golden.npz and ref_dispatch.json from the reference's own Python code.
 
-Run once in a container that has the reference source tree (path in H3METAL_REF, default /root/reference):
+Run once where the reference source tree is available (path in H3METAL_REF; default: a `reference` directory next
+to this repository):
 
     python tests/golden/make_golden.py
 
@@ -19,8 +20,8 @@ import sys
 import numpy as np
 
 sys.dont_write_bytecode = True
-REF = os.environ.get("H3METAL_REF", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("H3METAL_REF", os.path.abspath(os.path.join(HERE, "..", "..", "..", "reference")))
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(REF, "tests"))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))

@@ -1,6 +1,7 @@
 """The reference's own kernel tests, unmodified, driven through the oracle's CPU stand-in for its Gpu object.
 
-Needs the reference source tree (H3METAL_REF, default /root/reference); skipped where it is absent. The
+Needs the reference source tree (H3METAL_REF; default: a `reference` directory next to this repository); skipped
+where it is absent. The
 reference's h3metal/ops.py then supplies padding, strides, the LoRA sequence and the parameter blocks, its
 tests/test_gemm.py and tests/test_ops.py supply data, expectations and tolerances, and only the arithmetic of the
 two kernels comes from the oracle."""
@@ -9,7 +10,8 @@ import sys
 
 import pytest
 
-REF = os.environ.get("H3METAL_REF", "/root/reference")
+REF = os.environ.get("H3METAL_REF", os.path.abspath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..",
+                                                                 "reference")))
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "h3metal")), reason="reference tree not present")
 
 
