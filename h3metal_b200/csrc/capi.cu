@@ -61,6 +61,7 @@ const char *status_text(int code) {
     case 3: return "epilogue timed out waiting for an accumulator";
     case 4: return "wind-down timed out waiting for copies in flight";
     case 5: return "rotate+quantise kernel timed out waiting for a row to arrive in shared memory";
+    case 6: return "self-test: the wait on a barrier nobody signals timed out";
     default: return "unknown device status";
   }
 }
@@ -560,6 +561,14 @@ int h3b_gemm_w8a8_lora_noalloc(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, 
     return -1;
   return gemm_enqueue(ctx, A, a_stride, W, w_stride, sw, sa, bias, C, c_dtype, c_stride, M, N, K, T, R, lora_B, b_stride,
                       R, lora_ranges, false);
+}
+
+int h3b_selftest_expire_wait(h3b_ctx *ctx) {
+  if (!ctx) return fail("null context");
+  cudaEvent_t ps = nullptr;
+  if (ctx->before_launch(&ps)) return -1;
+  // about a millisecond at the part's clocks: long enough to be a real wait, short enough for a test
+  return ctx->after_launch("self-test launch", h3b::launch_expire_wait(ctx->status_dev, 2000000LL, ctx->stream));
 }
 
 void h3b_commit(h3b_ctx *) {}

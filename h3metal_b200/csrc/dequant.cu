@@ -8,9 +8,26 @@
 #include <cuda_fp16.h>
 
 #include "kernels.h"
+#include "ptx.cuh"
 
 namespace h3b {
 namespace {
+
+// Self-test of the bounded-wait machinery: one CTA initialises an mbarrier that nothing will ever signal and waits
+// on it with a short limit. The wait must run out, leave its code in the status word and let the kernel return
+// normally (nothing traps, nothing hangs, the context stays usable).
+__global__ void expire_wait_kernel(int *status, long long limit_cycles) {
+  __shared__ unsigned long long bar;
+  __shared__ int cta_abort;
+  if (threadIdx.x == 0) {
+    cta_abort = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, &cta_abort, status, kStatusSelfTest, limit_cycles);
+  __syncthreads();
+}
 
 template <typename OUT_T> __device__ __forceinline__ OUT_T cvt_out(float v);
 template <> __device__ __forceinline__ float cvt_out<float>(float v) { return v; }
@@ -81,6 +98,11 @@ cudaError_t launch_typed(const int32_t *acc, long long acc_stride, const float *
 }
 
 }  // namespace
+
+cudaError_t launch_expire_wait(int *status, long long limit_cycles, cudaStream_t stream) {
+  expire_wait_kernel<<<1, 32, 0, stream>>>(status, limit_cycles);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_dequant_i32(const int32_t *acc, long long acc_stride, const float *sa, const float *sw,
                                const float *bias, void *out, int c_dtype, long long c_stride, int M, int N, int sms,

@@ -42,6 +42,9 @@ cudaError_t launch_dequant_i32(const int32_t *acc, long long acc_stride, const f
                                const float *bias, void *out, int c_dtype, long long c_stride, int M, int N, int sms,
                                cudaStream_t stream);
 
+// Self-test: a kernel whose bounded wait must expire after `limit_cycles` and report through the status word.
+cudaError_t launch_expire_wait(int *status, long long limit_cycles, cudaStream_t stream);
+
 // Everything one launch of the int8 product needs. Tensor maps are built by the caller (capi.cu) because they
 // need the driver entry point and are cached per context.
 struct GemmLaunch {

@@ -17,6 +17,7 @@ enum DeviceStatus : int {
   kStatusEpilogueTimeout = 3,   // epilogue waited too long for an accumulator
   kStatusDrainTimeout = 4,      // wind-down waited too long for copies in flight
   kStatusRotTimeout = 5,        // rotate+quantise kernel waited too long for a row to arrive in shared memory
+  kStatusSelfTest = 6,          // the self-test's wait on a barrier nobody signals ran out, as it must
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

@@ -74,6 +74,7 @@ def _signatures():
         "h3b_gemm_tile_n": (i32, [vp, i32, i32]),
         "h3b_gemm_set_policy": (i32, [vp, i32, i32, i32]),
         "h3b_rot_set_policy": (i32, [vp, i32, i32]),
+        "h3b_selftest_expire_wait": (i32, [vp]),
         "h3b_commit": (None, [vp]),
         "h3b_wait": (dbl, [vp]),
         "h3b_set_profile": (None, [vp, i32]),

@@ -179,6 +179,13 @@ H3B_API int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band, int pair);
  * geometry of h3metal/ops.py:193-197. Returns 0. */
 H3B_API int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target, int tma_stages);
 
+/* Self-test of the error path the kernels share. Every device-side wait in this library is bounded: when one runs
+ * out the kernel records a code in the context's status word, winds down and returns, and the next h3b_wait reports
+ * it (negative return, message in h3b_last_error) with the context still usable. This call launches a one-CTA kernel
+ * that waits about a millisecond on a barrier nothing signals, so that exactly that happens. The counterpart of a
+ * failed command buffer surfacing from h3_wait (src/capi.h:66-70, src/capi.mm:235-243). Returns 0 (the launch). */
+H3B_API int h3b_selftest_expire_wait(h3b_ctx *ctx);
+
 /* Nothing is deferred on CUDA, so commit only exists for interface parity. Replaces h3_commit (src/capi.h:65). */
 H3B_API void h3b_commit(h3b_ctx *ctx);
 /* Blocks until the work launched through this context is done. Returns the GPU seconds between the first launch

@@ -78,3 +78,23 @@ def test_kernels_outside_the_path_are_refused(gpu):
     k = gpu.kernel("gemm.metal", "gemm", WFMT=2, EPI=0, OUT_T="half")
     with pytest.raises(GpuError):
         gpu.launch(k, (1, 1, 1), (32, 1, 1), [None] * 8, pack("8i", 64, 128, 256, 256, 128, 256, 2, 128), params_index=8)
+
+
+def test_an_expired_device_wait_surfaces_at_wait_and_the_context_survives(gpu):
+    """Every device-side wait is bounded. The self-test kernel waits on a barrier nothing signals; the wait runs out,
+    the kernel returns normally, wait() raises with the recorded reason, and the same context then computes a correct
+    product (nothing trapped, nothing hung)."""
+    from h3metal_b200.gpu import lib
+    gpu.wait()
+    assert lib().h3b_selftest_expire_wait(gpu.ctx) == 0
+    with pytest.raises(GpuError, match="timed out"):
+        gpu.wait()
+    assert gpu.wait() == 0.0  # the status word was cleared
+    rng = np.random.default_rng(2)
+    a = rng.integers(-127, 128, size=(128, 256), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(64, 256), dtype=np.int8)
+    out = gpu.empty((128, 64), "i32")
+    ops.gemm(gpu, gpu.upload(a), ops.QWeight("q8", gpu.upload(w), gpu.upload(np.ones(64, np.float32)), 64, 256), out, 128,
+             sa=gpu.upload(np.ones(128, np.float32)), tile=(128, 64, 4))
+    gpu.wait()
+    assert np.array_equal(out.numpy(), gemm_ref.int32_product(a, w))
