@@ -447,6 +447,37 @@ def library_int8_probe():
     print(json.dumps(out), flush=True)
 
 
+def whole_block(args):
+    """Not the headline: one Z-Image-shaped block END TO END on one GPU (both quantising kernels with their norm
+    front end, the four int8 products, the fused residual update, and attention + q/k norm + rotary from PyTorch),
+    to show what share of a block the path is. Prints one JSON line."""
+    import torch
+    from h3metal_b200.gpu import Gpu
+    from h3metal_b200.zimage_block import ZImageBlock
+    gpu = Gpu(device=0)
+    M = 4608
+    blk = ZImageBlock(gpu, M, 3840, 30, 10240, block=128, seed=0)
+    x = gpu.wrap(torch.randn(blk.m_pad, 3840, device=gpu.torch_device))
+    pending = None
+    for _ in range(3):
+        pending = blk.forward(x, pending)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record(gpu.stream)
+    for _ in range(args.steps):
+        pending = blk.forward(x, pending)
+    end.record(gpu.stream)
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / args.steps
+    gpu.profile(True)
+    blk.forward(x, pending)
+    path_s = sum(s for _, s in gpu.profile_take())
+    gpu.profile(False)
+    print(json.dumps({"workload": "one Z-Image-Turbo-shaped block, M=4608, attention by PyTorch SDPA", "ms_per_block": ms,
+                      "tokens_per_s": M / (ms * 1e-3), "path_kernels_ms": path_s * 1e3,
+                      "path_share": path_s * 1e3 / ms}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -466,9 +497,14 @@ def main():
                     help="tp: reduce-scatter instead of all-reduce (every rank finishes its M / N_gpus rows)")
     ap.add_argument("--library-int8-probe", action="store_true",
                     help="time the vendor library's int8 and bf16 GEMMs on this GPU (a yardstick; runs nothing of the path)")
+    ap.add_argument("--whole-block", action="store_true",
+                    help="time one whole Z-Image-shaped block with PyTorch attention (context for the path's share)")
     args = ap.parse_args()
     if args.library_int8_probe:
         library_int8_probe()
+        return
+    if args.whole_block:
+        whole_block(args)
         return
 
     from h3metal_b200 import workloads

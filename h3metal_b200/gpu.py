@@ -257,6 +257,8 @@ class Gpu:
                      np.dtype(np.uint8): "u8", np.dtype(np.int32): "i32", np.dtype(np.uint32): "u32",
                      np.dtype(np.uint16): "bf16", np.dtype(np.int16): "i16"}[arr.dtype]
         host = np.ascontiguousarray(arr)
+        if not host.flags.writeable:  # e.g. a view of a read-only file mapping: torch wants a writable source
+            host = host.copy()
         raw = torch.from_numpy(host.view(np.uint8).reshape(-1))
         with torch.cuda.stream(self.stream):
             dev = raw.to(self.torch_device)

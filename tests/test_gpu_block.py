@@ -78,3 +78,27 @@ def test_linear_from_an_h3m_file_with_an_adapter(gpu, tmp_path):
         dense += quant.rotate_in(quant.bf16_to_f32(xh) * 1.0, signs, block).astype(np.float64) @ t.A.T.astype(np.float64) @ t.B.T.astype(np.float64)
     assert np.linalg.norm(got - dense) / np.linalg.norm(dense) < 0.03
     wf.close()
+
+
+def test_zimage_block_matches_fp32_pytorch(gpu):
+    """A whole Z-Image-shaped block (both quantising kernels, four int8 products, the fused residual update) against
+    the same block in fp32 PyTorch on the dequantised weights: the reference's mini-model bound of 2 % relative
+    error for int8 (tests/test_zimage_mini.py:43), with attention supplied by PyTorch on both sides."""
+    import torch
+    from h3metal_b200.zimage_block import ZImageBlock
+    M, D, heads, F = 320, 512, 4, 1024
+    blk = ZImageBlock(gpu, M, D, heads, F, block=128, seed=1)
+    gen = torch.Generator(device=gpu.torch_device)
+    gen.manual_seed(7)
+    x0 = torch.randn(blk.m_pad, D, generator=gen, device=gpu.torch_device)
+    x0[:, :3] *= 8.0  # outlier channels
+    x = gpu.wrap(x0.clone())
+    pending = blk.forward(x)
+    blk.flush(x, pending)
+    gpu.wait()
+    want = blk.reference_forward(x0[:M])
+    got = x.torch()[:M]
+    err = float((got - want).norm() / want.norm())
+    assert err < 0.02, err
+    delta = float((want - x0[:M]).norm() / x0[:M].norm())
+    assert delta > 0.2  # the block changes the stream by far more than the allowed error
