@@ -268,19 +268,14 @@ def run_ours(args, cfg, rank, world):
     tokens = cfg.M * world * args.steps
     value = tokens / (ms * 1e-3)
 
-    # ---- per-kernel durations for the roofline: the same steps with an event pair around every launch ---------------
+    # ---- per-kernel durations for the roofline: the step's product launches alone, then its rotate+quantise launches
+    # alone, each group K times back to back between one event pair (an event pair per launch would put the launch gaps
+    # of 15-microsecond kernels into the figure). With a LoRA term the group also holds the narrow T products.
     peaks = measured_peaks()
-    gemm_s = rot_s = 0.0
     gemm_ops = rot_bytes = 0
-    gpu.profile(True)
-    for _ in range(args.steps):
-        blk.step()
-    for name, sec in gpu.profile_take():
-        if name.startswith("gemm"):
-            gemm_s += sec
-        else:
-            rot_s += sec
-    gpu.profile(False)
+    blk.step()
+    gemm_s = timed(blk.gemm_only, args.steps) * 1e-3
+    rot_s = timed(blk.rot_only, args.steps) * 1e-3
     for l in blk.layers:
         gemm_ops += 2 * l.m_pad * l.wt.K * l.wt.N * args.steps
         rot_bytes += blk.M * ((4 if l.swiglu_in else 2) * l.wt.K + l.wt.K + 4) * args.steps

@@ -82,6 +82,19 @@ class BlockLinears:
             prev = layer(prev if x is None else x)
         return prev
 
+    def rot_only(self):
+        """Only the rotate+quantise launches of a step (each on the input the step gives it)."""
+        prev = None
+        for layer, x in zip(self.layers, self.inputs):
+            src = prev if x is None else x
+            ops.rot_q8(self.gpu, src, layer.a8, layer.sa, layer.M, layer.wt.K, swiglu=layer.swiglu_in, block=layer.block)
+            prev = layer.out
+
+    def gemm_only(self):
+        """Only the product launches of a step (on the codes the last rotate+quantise left in each layer's buffers)."""
+        for layer in self.layers:
+            ops.gemm(self.gpu, layer.a8, layer.wt, layer.out, layer.M, sa=layer.sa, tile=(128, 32, 4))
+
     # -- the same step for a caller whose activations live in host memory ------------------------------------------------
     def host_buffers(self):
         """Pinned host tensors for step_host(): one input per layer that reads its own input, one output per layer
