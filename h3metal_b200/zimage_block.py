@@ -73,9 +73,9 @@ class ZImageBlock:
         q, k, v = (qkv[:, i * D:(i + 1) * D].reshape(M, H, hd) for i in range(3))
         rms = lambda t, w: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + self.eps) * w  # noqa: E731
         q, k = self._rope(rms(q, self.q_norm)), self._rope(rms(k, self.k_norm))
-        o = torch.nn.functional.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
-                                                             v.transpose(0, 1)[None])
-        return o[0].transpose(0, 1).reshape(M, D)
+        to = lambda t: t.transpose(0, 1)[None].to(torch.bfloat16)  # noqa: E731  (flash attention runs on bf16)
+        o = torch.nn.functional.scaled_dot_product_attention(to(q), to(k), to(v))
+        return o[0].transpose(0, 1).reshape(M, D).float()
 
     # -- the block on the quantised path ---------------------------------------------------------------------------
     def forward(self, x, pending=None):
