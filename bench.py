@@ -401,6 +401,21 @@ def run_tensor_parallel(args, cfg, rank, world, gpu):
     torch.cuda.synchronize(dev)
     ms = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    # where the step's time goes: one event pair per layer (its rotate+quantise, product and communication), max over ranks
+    n_layers = len(blk.layers)
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(n_layers + 1)] for _ in range(args.steps)]
+    dist.barrier()
+    torch.cuda.synchronize(dev)
+    for s in range(args.steps):
+        prev = None
+        for i, (layer, x) in enumerate(zip(blk.layers, blk.inputs)):
+            marks[s][i].record(gpu.stream)
+            prev = layer(prev if x is None else x)
+        marks[s][n_layers].record(gpu.stream)
+    torch.cuda.synchronize(dev)
+    per_layer = torch.tensor([sum(marks[s][i].elapsed_time(marks[s][i + 1]) for s in range(args.steps)) / args.steps
+                              for i in range(n_layers)], device=dev, dtype=torch.float64)
+    dist.all_reduce(per_layer, op=dist.ReduceOp.MAX)
     gpu.wait()
     if rank != 0:
         return None
@@ -411,7 +426,10 @@ def run_tensor_parallel(args, cfg, rank, world, gpu):
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": workload_name(cfg), "block": cfg.block,
                        "parallelism": f"tp{world}: column-parallel qkv/w1w3, row-parallel out/w2 ({args.reduce} {'reduce-scatter' if args.scatter else 'all-reduce'})"},
-            "tops": value / cfg.M * cfg.ops / 1e12, "gpu_launches": None}
+            "tops": value / cfg.M * cfg.ops / 1e12,
+            "layer_ms": {f"{spec.K}->{spec.N} ({spec.parallel})": round(float(t), 4)
+                         for spec, t in zip(cfg.layers, per_layer.tolist())},
+            "gpu_launches": None}
 
 
 def library_int8_probe():
@@ -486,8 +504,10 @@ def main():
     ap.add_argument("--parallel", default="token", choices=["token", "tp"],
                     help="N > 1: token = every rank its own M tokens (default, weak scaling); tp = ONE block of M tokens "
                          "sharded column-/row-parallel over the ranks with NCCL all-reduces (strong scaling)")
-    ap.add_argument("--reduce", default="int32", choices=["int32", "f32", "bf16"],
-                    help="tp: what the row-parallel layers all-reduce (int32 = bit-exact)")
+    ap.add_argument("--reduce", default="int32", choices=["int32", "f32", "bf16", "push", "push_bf16"],
+                    help="tp: what the row-parallel layers reduce (int32 = bit-exact, NCCL; push = bit-exact, partial "
+                         "accumulators stored by the product kernel straight into the row owners' memory over NVLink; "
+                         "push_bf16 = the same with bf16 partials)")
     ap.add_argument("--scatter", action="store_true",
                     help="tp: reduce-scatter instead of all-reduce (every rank finishes its M / N_gpus rows)")
     ap.add_argument("--library-int8-probe", action="store_true",

@@ -62,6 +62,7 @@ const char *status_text(int code) {
     case 4: return "wind-down timed out waiting for copies in flight";
     case 5: return "rotate+quantise kernel timed out waiting for a row to arrive in shared memory";
     case 6: return "self-test: the wait on a barrier nobody signals timed out";
+    case 7: return "rendezvous of a row-parallel layer timed out: another GPU did not signal";
     default: return "unknown device status";
   }
 }
@@ -410,8 +411,22 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
                         const float *sw, const float *sa, const float *bias, void *C, int c_dtype, int64_t c_stride,
                         int M, int N, int K, const void *lora_T, int64_t t_stride, const void *lora_B,
                         int64_t b_stride, int R, const int32_t *lora_ranges, bool cached_maps,
-                        const uint8_t *rtype = nullptr, const float *gate = nullptr, int64_t g_stride = 0) {
+                        const uint8_t *rtype = nullptr, const float *gate = nullptr, int64_t g_stride = 0,
+                        void *const *push_slots = nullptr, int push_world = 0, int push_rows = 0) {
   if (!ctx) return fail("null context");
+  const bool push = push_slots != nullptr;
+  if (push) {
+    if (push_world < 1 || push_world > h3b::kMaxPeers) return fail("gemm (push): 1 to 8 GPUs");
+    if (push_rows <= 0 || push_rows % 128) return fail("gemm (push): every GPU owns a multiple of 128 rows");
+    if (static_cast<long long>(push_rows) * push_world != M) return fail("gemm (push): M must equal rows_per_gpu x world");
+    if (c_dtype != H3B_I32 && c_dtype != H3B_BF16) return fail("gemm (push): staging holds int32 accumulators or bf16 partials");
+    if (N % 32) return fail("gemm (push): N must be a multiple of 32");
+    if ((c_stride * (c_dtype == H3B_I32 ? 4 : 2)) % 16) return fail("gemm (push): staging rows must be multiples of 16 bytes");
+    for (int i = 0; i < push_world; ++i)
+      if (!push_slots[i] || reinterpret_cast<uintptr_t>(push_slots[i]) % 16) return fail("gemm (push): null or misaligned slot");
+    if (lora_T || gate) return fail("gemm (push): no low-rank term and no gated epilogue on a row-parallel layer");
+    C = push_slots[0];
+  }
   if (!A || !W || !C) return fail("gemm: null tensor argument");
   if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: M, N and K must be positive");
   const bool raw = c_dtype == H3B_I32;
@@ -434,9 +449,10 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
   // Single CTAs (128 x tile_n tiles) by default. CTA pairs (256 x 256 tiles, B operand shared across the pair) are
   // available on request: measured on B200 they match the single-CTA kernel at the models' shapes and trail it on the
   // largest ones, the product being limited by the board's power cap rather than by shared-memory traffic.
-  const bool pair = !lora && ctx->pair_clusters > 0 && ctx->pair_mode == 1 && !ctx->tile_n_override;
+  const bool pair = !lora && !push && ctx->pair_clusters > 0 && ctx->pair_mode == 1 && !ctx->tile_n_override;
   const int bn = pair ? 128 : h3b_gemm_tile_n(ctx, N, lora);  // rows of W one CTA stages per K block
-  const int stages = pair ? ctx->pair_stages : h3b::gemm_pick_stages(bn, lora ? R : 0, ctx->prop.sharedMemPerBlockOptin);
+  const int stages = pair ? ctx->pair_stages
+                          : h3b::gemm_pick_stages(bn, lora ? R : 0, ctx->prop.sharedMemPerBlockOptin, push);
   if (stages < 2) return fail("gemm: tile does not fit the device's shared memory");
 
   h3b::GemmLaunch g;
@@ -459,6 +475,10 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
     if (g_stride < N) return fail("gemm: g_stride smaller than N");
   }
   g.rtype = rtype; g.gate = gate; g.g_stride = g_stride;
+  if (push) {
+    for (int i = 0; i < push_world; ++i) g.peer_c[i] = push_slots[i];
+    g.peer_rows = push_rows;
+  }
   g.sw = sw; g.sa = sa; g.bias = raw ? nullptr : bias; g.c = C; g.ranges = lora ? lora_ranges : nullptr;
   g.c_stride = c_stride; g.c_dtype = c_dtype; g.M = M; g.N = N; g.K = K; g.R = lora ? R : 0; g.bn = bn;
   g.acc_stages = (lora && bn == 256) ? 1 : 2;
@@ -503,6 +523,118 @@ int h3b_gemm_w8a8_gated(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
   if (!gate) return fail("gemm (gated): null gate table");
   return gemm_enqueue(ctx, A, a_stride, W, w_stride, sw, sa, bias, X, H3B_F32, c_stride, M, N, K, lora_T, t_stride, lora_B,
                       b_stride, R, lora_ranges, true, rtype, gate, g_stride);
+}
+
+// ---- row-parallel layers over the GPUs of one node -----------------------------------------------------------------
+void *h3b_peer_alloc(h3b_ctx *ctx, uint64_t bytes) {
+  if (!ctx || bytes == 0) {
+    fail("peer_alloc: null context or zero size");
+    return nullptr;
+  }
+  if (ctx->make_current()) return nullptr;
+  void *p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();  // the zeros are in place before the address leaves this call
+  if (e != cudaSuccess) {
+    if (p) cudaFree(p);
+    fail_cuda("peer_alloc", e);
+    return nullptr;
+  }
+  return p;
+}
+
+int h3b_peer_free(h3b_ctx *ctx, void *ptr) {
+  if (!ctx) return fail("null context");
+  if (ctx->make_current()) return -1;
+  const cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? 0 : fail_cuda("peer_free", e);
+}
+
+int h3b_peer_export(h3b_ctx *ctx, void *ptr, unsigned char handle[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the C ABI passes IPC handles as 64 bytes");
+  if (!ctx || !ptr || !handle) return fail("peer_export: null argument");
+  if (ctx->make_current()) return -1;
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) return fail_cuda("cudaIpcGetMemHandle", e);
+  memcpy(handle, &h, 64);
+  return 0;
+}
+
+void *h3b_peer_import(h3b_ctx *ctx, const unsigned char handle[64]) {
+  if (!ctx || !handle) {
+    fail("peer_import: null argument");
+    return nullptr;
+  }
+  if (ctx->make_current()) return nullptr;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void *p = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    fail_cuda("cudaIpcOpenMemHandle", e);
+    return nullptr;
+  }
+  return p;
+}
+
+int h3b_peer_unmap(h3b_ctx *ctx, void *ptr) {
+  if (!ctx) return fail("null context");
+  if (ctx->make_current()) return -1;
+  const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? 0 : fail_cuda("cudaIpcCloseMemHandle", e);
+}
+
+int h3b_peer_sync(h3b_ctx *ctx, void *const *flags, int rank, int world, uint32_t epoch, int mode) {
+  if (!ctx || !flags) return fail("peer_sync: null argument");
+  if (world < 1 || world > h3b::kMaxPeers || rank < 0 || rank >= world) return fail("peer_sync: bad rank / world");
+  if (mode < 0 || mode > 2) return fail("peer_sync: mode must be 0 (signal and wait), 1 (signal) or 2 (wait)");
+  h3b::PeerSync p = {};
+  for (int i = 0; i < world; ++i) {
+    if (!flags[i] || reinterpret_cast<uintptr_t>(flags[i]) % 4) return fail("peer_sync: null or misaligned flag array");
+    p.flags[i] = static_cast<unsigned int *>(flags[i]);
+  }
+  p.rank = rank; p.world = world; p.mode = mode; p.epoch = epoch; p.status = ctx->status_dev;
+  p.limit_cycles = 2000000000LL;  // about a second at the part's clocks
+  cudaEvent_t ps = nullptr;
+  if (ctx->before_launch(&ps)) return -1;
+  return ctx->after_launch("peer_sync launch", h3b::launch_peer_sync(p, ctx->stream));
+}
+
+int h3b_gemm_w8a8_push(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
+                       const float *sw, const float *sa, void *const *slots, int world, int rows_per_gpu,
+                       int stage_dtype, int64_t stage_stride, int M, int N, int K) {
+  if (!slots) return fail("gemm (push): null slot table");
+  return gemm_enqueue(ctx, A, a_stride, W, w_stride, sw, sa, nullptr, nullptr, stage_dtype, stage_stride, M, N, K, nullptr, 0,
+                      nullptr, 0, 0, nullptr, true, nullptr, nullptr, 0, slots, world, rows_per_gpu);
+}
+
+int h3b_reduce_dequant(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride, int stage_dtype,
+                       int world, const float *sa, const float *sw, const float *bias, void *const *outs, int n_out,
+                       int c_dtype, int64_t c_stride, int rows, int N, int row0) {
+  if (!ctx) return fail("null context");
+  if (!stage || !outs) return fail("reduce_dequant: null tensor argument");
+  if (world < 1 || world > h3b::kMaxPeers || n_out < 1 || n_out > h3b::kMaxPeers) return fail("reduce_dequant: 1 to 8 slots and outputs");
+  if (stage_dtype != H3B_I32 && stage_dtype != H3B_BF16) return fail("reduce_dequant: staging holds int32 or bf16");
+  if (stage_dtype == H3B_I32 && (!sa || !sw)) return fail("reduce_dequant: int32 partials need the row and column scales");
+  if (c_dtype != H3B_BF16 && c_dtype != H3B_F16 && c_dtype != H3B_F32) return fail("reduce_dequant: output type must be bf16, f16 or f32");
+  if (rows <= 0 || N <= 0 || N % 8 || stage_stride < N || c_stride < N || row0 < 0) return fail("reduce_dequant: bad sizes (N must be a multiple of 8)");
+  const int ss = stage_dtype == H3B_I32 ? 4 : 2, cs = c_dtype == H3B_F32 ? 4 : 2;
+  if (reinterpret_cast<uintptr_t>(stage) % 16 || (stage_stride * ss) % 16 || (slot_stride * ss) % 16 || (c_stride * cs) % 16 ||
+      (sw && reinterpret_cast<uintptr_t>(sw) % 16) || (bias && reinterpret_cast<uintptr_t>(bias) % 16))
+    return fail("reduce_dequant: tensors must be 16-byte aligned with strides that are multiples of 16 bytes");
+  h3b::ReduceLaunch r = {};
+  r.stage = stage; r.slot_stride = slot_stride; r.stage_stride = stage_stride; r.stage_dtype = stage_dtype; r.world = world;
+  r.sa = sa; r.sw = sw; r.bias = bias; r.n_out = n_out; r.c_stride = c_stride; r.c_dtype = c_dtype; r.rows = rows; r.N = N;
+  r.row0 = row0;
+  for (int i = 0; i < n_out; ++i) {
+    if (!outs[i] || reinterpret_cast<uintptr_t>(outs[i]) % 16) return fail("reduce_dequant: null or misaligned output");
+    r.out[i] = outs[i];
+  }
+  cudaEvent_t ps = nullptr;
+  if (ctx->before_launch(&ps)) return -1;
+  return ctx->after_launch("reduce_dequant launch", h3b::launch_reduce_dequant(r, ctx->prop.multiProcessorCount, ctx->stream));
 }
 
 // ---- the product with a LoRA term for callers that cannot allocate ------------------------------------------------

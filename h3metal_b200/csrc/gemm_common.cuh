@@ -22,6 +22,7 @@ constexpr int kTmemCols = 512;
 constexpr int kLowBase = 256;       // first TMEM column of the LoRA accumulators
 constexpr int kThreads = 192;
 constexpr int kBarrierBytes = 256;
+constexpr int kPushBytes = 4 * 4096;  // row-parallel push: a 32 x 32-word transposition buffer per epilogue warp
 
 __host__ __device__ constexpr int stage_bytes(int bn) { return kABytes + bn * kBKBytes; }
 __host__ __device__ constexpr int lora_bytes(int bn, int R) { return (R / kLoraChunk) * (kLoraTBytes + bn * kLoraChunk * 2); }
@@ -99,6 +100,34 @@ __device__ __forceinline__ void store_segment(OUT_T *dst, const float (&v)[32], 
   }
 }
 
+// float(acc) * sa * sw (+ bias) (+ low) for 32 columns, two at a time with the packed fp32 instructions (each half is
+// rounded exactly like the scalar operation): convert, times the row scale, times the column scale, plus bias,
+// plus the low-rank term.
+__device__ __forceinline__ void dequant32(const GemmLaunch &g, const uint32_t (&acc)[32], const uint32_t (&low)[32],
+                                          bool has_low, float sa_m, const float *sw_s, const float *bias_s,
+                                          float (&v)[32]) {
+  const bool has_bias = g.bias != nullptr;
+  const float2 sa2 = make_float2(sa_m, sa_m);
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 w4 = *reinterpret_cast<const float4 *>(sw_s + j);
+    const float4 b4 = *reinterpret_cast<const float4 *>(bias_s + j);
+    float2 x0 = make_float2(__int2float_rn(static_cast<int32_t>(acc[j])), __int2float_rn(static_cast<int32_t>(acc[j + 1])));
+    float2 x1 = make_float2(__int2float_rn(static_cast<int32_t>(acc[j + 2])), __int2float_rn(static_cast<int32_t>(acc[j + 3])));
+    x0 = __fmul2_rn(__fmul2_rn(x0, sa2), make_float2(w4.x, w4.y));
+    x1 = __fmul2_rn(__fmul2_rn(x1, sa2), make_float2(w4.z, w4.w));
+    if (has_bias) {
+      x0 = __fadd2_rn(x0, make_float2(b4.x, b4.y));
+      x1 = __fadd2_rn(x1, make_float2(b4.z, b4.w));
+    }
+    if (has_low) {
+      x0 = __fadd2_rn(x0, make_float2(__uint_as_float(low[j]), __uint_as_float(low[j + 1])));
+      x1 = __fadd2_rn(x1, make_float2(__uint_as_float(low[j + 2]), __uint_as_float(low[j + 3])));
+    }
+    v[j] = x0.x; v[j + 1] = x0.y; v[j + 2] = x1.x; v[j + 3] = x1.y;
+  }
+}
+
 // Finishes 32 accumulator columns [n, n + 32) of row m: either the raw int32 values, or the dequantising
 // epilogue float(acc) * sa * sw (+ bias) (+ low) in the reference's operation order, converted to the output type
 // or, with a gate table, accumulated into the fp32 residual stream (the reference's epilogue 1,
@@ -123,29 +152,8 @@ __device__ __forceinline__ void finish_chunk(const GemmLaunch &g, const uint32_t
     }
     return;
   }
-  // Two columns at a time with the packed fp32 instructions (each half is rounded exactly like the scalar
-  // operation): convert, times the row scale, times the column scale, plus bias, plus the low-rank term.
-  const bool has_bias = g.bias != nullptr;
-  const float2 sa2 = make_float2(sa_m, sa_m);
   float v[32];
-#pragma unroll
-  for (int j = 0; j < 32; j += 4) {
-    const float4 w4 = *reinterpret_cast<const float4 *>(sw_s + j);
-    const float4 b4 = *reinterpret_cast<const float4 *>(bias_s + j);
-    float2 x0 = make_float2(__int2float_rn(static_cast<int32_t>(acc[j])), __int2float_rn(static_cast<int32_t>(acc[j + 1])));
-    float2 x1 = make_float2(__int2float_rn(static_cast<int32_t>(acc[j + 2])), __int2float_rn(static_cast<int32_t>(acc[j + 3])));
-    x0 = __fmul2_rn(__fmul2_rn(x0, sa2), make_float2(w4.x, w4.y));
-    x1 = __fmul2_rn(__fmul2_rn(x1, sa2), make_float2(w4.z, w4.w));
-    if (has_bias) {
-      x0 = __fadd2_rn(x0, make_float2(b4.x, b4.y));
-      x1 = __fadd2_rn(x1, make_float2(b4.z, b4.w));
-    }
-    if (has_low) {
-      x0 = __fadd2_rn(x0, make_float2(__uint_as_float(low[j]), __uint_as_float(low[j + 1])));
-      x1 = __fadd2_rn(x1, make_float2(__uint_as_float(low[j + 2]), __uint_as_float(low[j + 3])));
-    }
-    v[j] = x0.x; v[j + 1] = x0.y; v[j + 2] = x1.x; v[j + 3] = x1.y;
-  }
+  dequant32(g, acc, low, has_low, sa_m, sw_s, bias_s, v);
   const size_t off = static_cast<size_t>(m) * g.c_stride + n;
   if (g.gate != nullptr) {
     // gated-residual epilogue: X[m][n] += gate[type[m]][n] * v, X the fp32 residual stream (one multiply, one add)
@@ -171,6 +179,50 @@ __device__ __forceinline__ void finish_chunk(const GemmLaunch &g, const uint32_t
   if (g.c_dtype == kDtypeBf16) store_segment(static_cast<__nv_bfloat16 *>(g.c) + off, v, n_valid, vec_ok);
   else if (g.c_dtype == kDtypeF16) store_segment(static_cast<__half *>(g.c) + off, v, n_valid, vec_ok);
   else store_segment(static_cast<float *>(g.c) + off, v, n_valid, vec_ok);
+}
+
+// Row-parallel push: the warp's 32 rows x 32 columns [n, n + 32) of this GPU's partial product go to the staging
+// slot of the rows' owner, which may be another GPU (plain stores through a peer mapping). A lane holds one ROW of
+// the chunk, so a direct store would touch 32 rows with 16 bytes each; over NVLink that is 32 small packets. The chunk
+// is therefore transposed through the warp's 4 KB of shared memory first: afterwards eight (int32) or four (bf16)
+// neighbouring lanes hold one row's 128 or 64 contiguous bytes and every store instruction writes whole lines.
+// `xpose` is the warp's own buffer; 16-byte piece k of row r sits at piece k ^ (r & 7) so that both the row-wise
+// writes and the line-wise reads spread over the banks. dst_rows points at row 0 of the tile's 128 rows in the slot.
+__device__ __forceinline__ void push_chunk(const GemmLaunch &g, const uint32_t (&acc)[32], int quarter, int lane, int n,
+                                           float sa_m, const float *sw_s, const float *bias_s, uint4 *xpose,
+                                           uint8_t *dst_rows) {
+  if (n >= g.N) return;  // a column tile hanging over N (N is a multiple of 32: chunks are whole or absent)
+  const uint32_t no_low[32] = {};
+  __syncwarp();
+  if (g.c_dtype == kDtypeI32) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      xpose[lane * 8 + (k ^ (lane & 7))] = make_uint4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // four rows per instruction, eight lanes (128 bytes) per row
+      const int r = 4 * i + (lane >> 3), k = lane & 7;
+      const uint4 q = xpose[r * 8 + (k ^ (r & 7))];
+      uint8_t *row = dst_rows + static_cast<size_t>(quarter * 32 + r) * g.c_stride * 4;
+      *reinterpret_cast<uint4 *>(row + static_cast<size_t>(n) * 4 + k * 16) = q;
+    }
+  } else {  // bf16 partials: float(acc) * sa * sw, no bias (the owner adds it once)
+    float v[32];
+    dequant32(g, acc, no_low, false, sa_m, sw_s, bias_s, v);
+    uint32_t w[32];
+    Packed<__nv_bfloat16>::pack(v, w);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      xpose[lane * 8 + (k ^ (lane & 7))] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // eight rows per instruction, four lanes (64 bytes) per row
+      const int r = 8 * i + (lane >> 2), k = lane & 3;
+      const uint4 q = xpose[r * 8 + (k ^ (r & 7))];
+      uint8_t *row = dst_rows + static_cast<size_t>(quarter * 32 + r) * g.c_stride * 2;
+      *reinterpret_cast<uint4 *>(row + static_cast<size_t>(n) * 2 + k * 16) = q;
+    }
+  }
 }
 
 // Stages the column scales and biases of columns [n0, n0 + bn) in a warp's own slice of shared memory.

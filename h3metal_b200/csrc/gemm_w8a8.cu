@@ -33,10 +33,11 @@ namespace {
 
 using namespace gemm;
 
-template <int BN, int ACC_STAGES, bool LORA, int EPI_WARPS>
+template <int BN, int ACC_STAGES, bool LORA, int EPI_WARPS, bool PUSH = false>
 __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const __grid_constant__ GemmLaunch g,
                                                                            const int stages) {
   static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "one or two epilogue warps per TMEM lane quarter");
+  static_assert(!(PUSH && (LORA || EPI_WARPS != 4)), "the row-parallel push has no low-rank term");
   static_assert(ACC_STAGES * BN <= (LORA ? kLowBase : kTmemCols), "accumulators do not fit tensor memory");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -59,6 +60,8 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
   volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(base_ptr + bars_off + 176);
   volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + bars_off + 180);
   float *col_stage = reinterpret_cast<float *>(base_ptr + bars_off + kBarrierBytes);  // [EPI_WARPS][2][BN]: sw, bias
+  // PUSH: 4 KB per epilogue warp behind the column staging, for the transposition of outgoing chunks
+  uint4 *xpose_all = reinterpret_cast<uint4 *>(base_ptr + bars_off + kBarrierBytes + 16 * BN * sizeof(float));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (g.M + kBM - 1) / kBM, n_tiles = (g.N + BN - 1) / BN;
@@ -226,6 +229,18 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
         }
         has_low = k1 > k0;
       }
+      uint4 *xpose = nullptr;
+      uint8_t *push_rows = nullptr;  // PUSH: row 0 of this tile in the owner's staging slot
+      if constexpr (PUSH) {
+        const int owner = m0 / g.peer_rows;
+        xpose = xpose_all + (warp - 2) * 256;
+        push_rows = static_cast<uint8_t *>(g.peer_c[owner]) +
+                    static_cast<size_t>(m0 - owner * g.peer_rows) * g.c_stride * (raw ? 4 : 2);
+      }
+      auto finish = [&](const uint32_t (&acc)[32], const uint32_t (&low)[32], int c) {
+        if constexpr (PUSH) push_chunk(g, acc, quarter, lane, n0 + c * 32, sa_m, sw_s + c * 32, bias_s + c * 32, xpose, push_rows);
+        else finish_chunk(g, acc, low, LORA && has_low, m, n0 + c * 32, sa_m, sw_s + c * 32, bias_s + c * 32, vec_ok);
+      };
       ok = mbar_wait(acc_full_bar(as), aph, cta_abort, g.status, kStatusEpilogueTimeout);
       if (!ok) break;
       tc_fence_after_sync();
@@ -242,12 +257,11 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
       for (int c = c_begin; c < c_end; c += 2) {
         tmem_ld_wait();
         if (c + 1 < c_end) fetch(c + 1, acc_b, low_b);
-        finish_chunk(g, acc_a, low_a, LORA && has_low, m, n0 + c * 32, sa_m, sw_s + c * 32, bias_s + c * 32, vec_ok);
+        finish(acc_a, low_a, c);
         if (c + 1 < c_end) {
           tmem_ld_wait();
           if (c + 2 < c_end) fetch(c + 2, acc_a, low_a);
-          finish_chunk(g, acc_b, low_b, LORA && has_low, m, n0 + (c + 1) * 32, sa_m, sw_s + (c + 1) * 32,
-                       bias_s + (c + 1) * 32, vec_ok);
+          finish(acc_b, low_b, c + 1);
         }
       }
       tc_fence_before_sync();
@@ -265,17 +279,17 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
   }
 }
 
-template <int BN, int ACC_STAGES, bool LORA, int EPI>
+template <int BN, int ACC_STAGES, bool LORA, int EPI, bool PUSH = false>
 cudaError_t launch_one(const GemmLaunch &g, int stages, cudaStream_t stream) {
-  const size_t smem = gemm_smem_bytes(BN, LORA ? g.R : 0, stages);
-  gemm_w8a8_kernel<BN, ACC_STAGES, LORA, EPI><<<g.grid, 64 + 32 * EPI, smem, stream>>>(g, stages);
+  const size_t smem = gemm_smem_bytes(BN, LORA ? g.R : 0, stages) + (PUSH ? kPushBytes : 0);
+  gemm_w8a8_kernel<BN, ACC_STAGES, LORA, EPI, PUSH><<<g.grid, 64 + 32 * EPI, smem, stream>>>(g, stages);
   return cudaGetLastError();
 }
 
-template <int BN, int ACC_STAGES, bool LORA, int EPI>
+template <int BN, int ACC_STAGES, bool LORA, int EPI, bool PUSH = false>
 cudaError_t configure_one() {
-  return cudaFuncSetAttribute(gemm_w8a8_kernel<BN, ACC_STAGES, LORA, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              232448);
+  return cudaFuncSetAttribute(gemm_w8a8_kernel<BN, ACC_STAGES, LORA, EPI, PUSH>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
 }
 
 }  // namespace
@@ -287,9 +301,9 @@ size_t gemm_smem_bytes(int bn, int R, int stages) {
          16 * static_cast<size_t>(bn) * sizeof(float);  // column staging for up to eight epilogue warps
 }
 
-int gemm_pick_stages(int bn, int R, size_t smem_optin) {
+int gemm_pick_stages(int bn, int R, size_t smem_optin, bool push) {
   for (int s = kMaxStages; s >= 2; --s) {
-    const size_t need = gemm_smem_bytes(bn, R, s);
+    const size_t need = gemm_smem_bytes(bn, R, s) + (push ? kPushBytes : 0);
     if (need != 0 && need <= smem_optin) return s;
   }
   return 0;
@@ -302,11 +316,25 @@ cudaError_t gemm_configure(int /*device*/) {
   H3B_CFG(32, 2, false, 4) H3B_CFG(64, 2, false, 4) H3B_CFG(128, 2, false, 4) H3B_CFG(256, 2, false, 4)
   H3B_CFG(32, 2, true, 4) H3B_CFG(64, 2, true, 4) H3B_CFG(128, 2, true, 4) H3B_CFG(256, 1, true, 4)
 #undef H3B_CFG
+#define H3B_CFG_PUSH(BN) \
+  if ((e = configure_one<BN, 2, false, 4, true>()) != cudaSuccess) return e;
+  H3B_CFG_PUSH(32) H3B_CFG_PUSH(64) H3B_CFG_PUSH(128) H3B_CFG_PUSH(256)
+#undef H3B_CFG_PUSH
   return cudaSuccess;
 }
 
 cudaError_t launch_gemm_w8a8(const GemmLaunch &g, int stages, cudaStream_t stream) {
   const bool lora = g.R > 0;
+  if (g.peer_rows > 0) {
+    if (lora) return cudaErrorInvalidValue;
+    switch (g.bn) {
+      case 32: return launch_one<32, 2, false, 4, true>(g, stages, stream);
+      case 64: return launch_one<64, 2, false, 4, true>(g, stages, stream);
+      case 128: return launch_one<128, 2, false, 4, true>(g, stages, stream);
+      case 256: return launch_one<256, 2, false, 4, true>(g, stages, stream);
+      default: return cudaErrorInvalidValue;
+    }
+  }
   switch (g.bn) {
     case 32: return lora ? launch_one<32, 2, true, 4>(g, stages, stream) : launch_one<32, 2, false, 4>(g, stages, stream);
     case 64: return lora ? launch_one<64, 2, true, 4>(g, stages, stream) : launch_one<64, 2, false, 4>(g, stages, stream);

@@ -9,6 +9,7 @@ namespace h3b {
 
 // Element types as the C ABI numbers them (include/h3b200.h).
 enum Dtype : int { kDtypeF32 = 0, kDtypeF16 = 1, kDtypeBf16 = 2, kDtypeI8 = 3, kDtypeI32 = 4 };
+constexpr int kMaxPeers = 8;  // GPUs of one node that may share a row-parallel layer
 
 void rot_q8_geometry(int D, int threads_target, int *ch, int *threads);
 cudaError_t launch_rot_q8(const void *x, int x_dtype, long long x_stride, void *out, float *sa, int M, int D,
@@ -42,6 +43,37 @@ cudaError_t launch_dequant_i32(const int32_t *acc, long long acc_stride, const f
                                const float *bias, void *out, int c_dtype, long long c_stride, int M, int N, int sms,
                                cudaStream_t stream);
 
+// Owner's side of the row-parallel push: out[m][n] = epilogue(sum over the `world` slots of stage[slot][m][n]) for
+// the owner's `rows` rows. stage_dtype kDtypeI32: int32 partial accumulators, summed exactly, then the product's
+// epilogue (* sa[m] * sw[n] + bias[n]). kDtypeBf16: dequantised bf16 partials, summed in fp32 in slot order, plus bias.
+// out_peers (or null): the finished rows are also stored into every GPU's copy of the output at row `row0` on (an
+// all-gather by peer stores); out_peers[rank] may be the local buffer.
+struct ReduceLaunch {
+  const void *stage;        // [world][rows][stage_stride] of stage_dtype
+  long long slot_stride;    // elements between slots
+  long long stage_stride;   // elements between rows
+  int stage_dtype, world;
+  const float *sa, *sw, *bias;
+  void *out[kMaxPeers];     // out[0] only, or one base per GPU (each [..][c_stride], rows written at row0 + m)
+  int n_out;
+  long long c_stride;
+  int c_dtype, rows, N, row0;
+};
+cudaError_t launch_reduce_dequant(const ReduceLaunch &r, int sms, cudaStream_t stream);
+
+// Cross-GPU rendezvous on flag words in peer-mapped memory. flags[q] points at GPU q's array of `world` 32-bit words;
+// this GPU (index `rank`) stores `epoch` into word `rank` of every GPU's array (mode 0 or 1) and then waits, for at
+// most about a second, until every word of its own array has reached `epoch` (mode 0 or 2). A wait that runs out
+// leaves kStatusPeerTimeout in the status word and the kernel returns; nothing spins for ever.
+struct PeerSync {
+  unsigned int *flags[kMaxPeers];
+  int rank, world, mode;
+  unsigned int epoch;
+  int *status;
+  long long limit_cycles;
+};
+cudaError_t launch_peer_sync(const PeerSync &p, cudaStream_t stream);
+
 // Self-test: a kernel whose bounded wait must expire after `limit_cycles` and report through the status word.
 cudaError_t launch_expire_wait(int *status, long long limit_cycles, cudaStream_t stream);
 
@@ -69,12 +101,20 @@ struct GemmLaunch {
   int band;            // row tiles swept per column tile before moving on (L2 reuse)
   int grid;            // CTAs (persistent)
   int *status;         // device status word of the context
+  // Row-parallel push (K-sharded layers over several GPUs): rows [o * peer_rows, (o + 1) * peer_rows) of the result
+  // belong to GPU o, and this GPU's partial product of those rows is stored straight into peer_c[o], its slot
+  // [peer_rows][c_stride] in o's staging memory (a peer mapping; o == this GPU for its own rows). c_dtype is then
+  // kDtypeI32 (raw partial accumulators, summed exactly by the owner) or kDtypeBf16 (dequantised partials without
+  // bias). peer_rows == 0: no push, `c` is used.
+  void *peer_c[kMaxPeers];
+  int peer_rows;
 };
 
 // Shared memory a launch with this tile width and rank needs for `stages` operand stages; 0 if unsupported.
 size_t gemm_smem_bytes(int bn, int R, int stages);
-// Largest stage count (<= 8) that fits the device's opt-in shared memory, or 0.
-int gemm_pick_stages(int bn, int R, size_t smem_optin);
+// Largest stage count (<= 8) that fits the device's opt-in shared memory, or 0. push: the row-parallel push's
+// transposition buffers are part of the launch.
+int gemm_pick_stages(int bn, int R, size_t smem_optin, bool push = false);
 cudaError_t gemm_configure(int device);  // raises the dynamic shared-memory limit of every instantiation
 cudaError_t launch_gemm_w8a8(const GemmLaunch &g, int stages, cudaStream_t stream);
 

@@ -18,6 +18,7 @@ enum DeviceStatus : int {
   kStatusDrainTimeout = 4,      // wind-down waited too long for copies in flight
   kStatusRotTimeout = 5,        // rotate+quantise kernel waited too long for a row to arrive in shared memory
   kStatusSelfTest = 6,          // the self-test's wait on a barrier nobody signals ran out, as it must
+  kStatusPeerTimeout = 7,       // another GPU of a row-parallel layer did not signal within the limit
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

@@ -71,6 +71,15 @@ def _signatures():
                                       i32, vp]),
         "h3b_gemm_w8a8_lora_noalloc": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32, i32, vp, i64, vp,
                                              vp, i64, i32, vp]),
+        "h3b_peer_alloc": (vp, [vp, u64]),
+        "h3b_peer_free": (i32, [vp, vp]),
+        "h3b_peer_export": (i32, [vp, vp, ctypes.c_char_p]),
+        "h3b_peer_import": (vp, [vp, ctypes.c_char_p]),
+        "h3b_peer_unmap": (i32, [vp, vp]),
+        "h3b_peer_sync": (i32, [vp, ctypes.POINTER(vp), i32, i32, ctypes.c_uint32, i32]),
+        "h3b_gemm_w8a8_push": (i32, [vp, vp, i64, vp, i64, vp, vp, ctypes.POINTER(vp), i32, i32, i32, i64, i32, i32, i32]),
+        "h3b_reduce_dequant": (i32, [vp, vp, i64, i64, i32, i32, vp, vp, vp, ctypes.POINTER(vp), i32, i32, i64, i32, i32,
+                                     i32]),
         "h3b_gemm_tile_n": (i32, [vp, i32, i32]),
         "h3b_gemm_set_policy": (i32, [vp, i32, i32, i32]),
         "h3b_rot_set_policy": (i32, [vp, i32, i32]),
@@ -339,6 +348,69 @@ class Gpu:
                                                b_stride, R, ranges_ptr))
         if self._profile:
             self.names.append(name)
+
+    # -- row-parallel layers: peer-mapped memory, rendezvous, push and the owner's reduction ------------------------------
+    def peer_alloc(self, nbytes: int) -> Tensor:
+        """Zero-filled device memory that other processes can map (u8 [nbytes])."""
+        ptr = lib().h3b_peer_alloc(self.ctx, int(nbytes))
+        if not ptr:
+            raise GpuError(_err())
+        return self.wrap_ptr(int(ptr), int(nbytes))
+
+    def wrap_ptr(self, ptr: int, nbytes: int) -> Tensor:
+        """A u8 Tensor over raw device memory this process can address (its own or a peer mapping); not owned."""
+        torch = _torch()
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+        t = torch.as_tensor(_Raw(), device=self.torch_device)
+        return Tensor(Buffer(int(ptr), int(nbytes), owner=t), 0, (int(nbytes),), "u8")
+
+    def peer_free(self, ptr: int):
+        self._check(lib().h3b_peer_free(self.ctx, ctypes.c_void_p(ptr)))
+
+    def peer_export(self, ptr: int) -> bytes:
+        handle = ctypes.create_string_buffer(64)
+        self._check(lib().h3b_peer_export(self.ctx, ctypes.c_void_p(ptr), handle))
+        return handle.raw
+
+    def peer_import(self, handle: bytes) -> int:
+        ptr = lib().h3b_peer_import(self.ctx, ctypes.create_string_buffer(bytes(handle), 64))
+        if not ptr:
+            raise GpuError(_err())
+        return int(ptr)
+
+    def peer_unmap(self, ptr: int):
+        self._check(lib().h3b_peer_unmap(self.ctx, ctypes.c_void_p(ptr)))
+
+    @staticmethod
+    def _ptr_array(ptrs):
+        return (ctypes.c_void_p * len(ptrs))(*[ctypes.c_void_p(int(p)) for p in ptrs])
+
+    def peer_sync_native(self, flags, rank: int, world: int, epoch: int, mode: int = 0):
+        self._check(lib().h3b_peer_sync(self.ctx, self._ptr_array(flags), rank, world, epoch & 0xFFFFFFFF, mode))
+        if self._profile:
+            self.names.append("peer_sync")
+
+    def gemm_push_native(self, a: Tensor, a_stride: int, w: Tensor, w_stride: int, sw: Tensor | None, sa: Tensor | None,
+                         slots, rows_per_gpu: int, stage_dtype: str, stage_stride: int, M: int, N: int, K: int):
+        p = lambda t: t.ptr if t is not None else None  # noqa: E731
+        self._check(lib().h3b_gemm_w8a8_push(self.ctx, a.ptr, a_stride, w.ptr, w_stride, p(sw), p(sa),
+                                              self._ptr_array(slots), len(slots), rows_per_gpu, _ABI_DTYPE[stage_dtype],
+                                              stage_stride, M, N, K))
+        if self._profile:
+            self.names.append("gemm(push)")
+
+    def reduce_dequant_native(self, stage_ptr: int, slot_stride: int, stage_stride: int, stage_dtype: str, world: int,
+                              sa_ptr: int | None, sw: Tensor | None, bias: Tensor | None, outs, out_dtype: str,
+                              c_stride: int, rows: int, N: int, row0: int = 0):
+        p = lambda t: t.ptr if t is not None else None  # noqa: E731
+        self._check(lib().h3b_reduce_dequant(self.ctx, ctypes.c_void_p(stage_ptr), slot_stride, stage_stride,
+                                              _ABI_DTYPE[stage_dtype], world, ctypes.c_void_p(sa_ptr) if sa_ptr else None,
+                                              p(sw), p(bias), self._ptr_array(outs), len(outs), _ABI_DTYPE[out_dtype],
+                                              c_stride, rows, N, row0))
+        if self._profile:
+            self.names.append("reduce_dequant")
 
     def gemm_tile_n(self, N: int, lora: bool) -> int:
         return lib().h3b_gemm_tile_n(self.ctx, N, int(lora))

@@ -18,6 +18,13 @@ row-parallel    W's columns (K) are split; the input arrives already sharded on 
                 `scatter=True` step (5) is a reduce-scatter and every rank finishes only its M / p rows (what a
                 following per-token operation needs; half the traffic). A faster, approximate variant all-reduces
                 dequantised fp32 or bf16 partials instead (`reduce="f32" | "bf16"`).
+                `reduce="push"` (exact) and `reduce="push_bf16"` take the communication library off the data path:
+                the product kernel stores every finished tile of its partial accumulators straight into the staging
+                memory of the GPU that owns those rows (peer stores over NVLink, overlapping the rest of the
+                product), a bounded device-side rendezvous follows, and each owner sums its M / p rows, applies the
+                epilogue and - unless `scatter=True` - stores the finished bf16 rows into every GPU's output. Exact
+                int32 partials cross NVLink once (reduce-scatter) and the all-gather moves 2-byte outputs, a quarter
+                less traffic than an int32 all-reduce; `push_bf16` halves the first leg again.
                 K / p must be a multiple of the rotation block. A LoRA term on a row-parallel layer is not supported.
 
 Collectives run on torch's current stream, which is also the stream the kernels are launched on, so a layer is
@@ -71,6 +78,67 @@ def _put(gpu, t):
     if t is None:
         return None
     return gpu.upload(t) if isinstance(t, np.ndarray) else gpu.wrap(t)
+
+
+def push_layout(m_pad: int, N: int, world: int, stage_dtype: str, out_dtype: str | None):
+    """Byte layout of a rank's peer block for the push variants, after the flag words: two staging buffers (calls
+    alternate between them) of `world` slots [rows][N] each, then, if out_dtype is given, the full output [m_pad][N].
+    Returns (rows, slot_bytes, stage_bytes, out_offset, total_bytes)."""
+    if m_pad % (128 * world):
+        raise ValueError(f"{m_pad} rows do not split into {world} shards of whole 128-row tiles")
+    if N % 32:
+        raise ValueError(f"N = {N} is not a multiple of 32")
+    rows = m_pad // world
+    slot = rows * N * {"i32": 4, "bf16": 2}[stage_dtype]
+    stage = world * slot
+    out = m_pad * N * {"bf16": 2, "f16": 2, "f32": 4}[out_dtype] if out_dtype else 0
+    return rows, slot, stage, 2 * stage, 2 * stage + out
+
+
+class PeerBlock:
+    """One block of shareable device memory per rank of `group`, with every other rank's block mapped into this
+    process (CUDA IPC; peer access over NVLink). The first 256 bytes of a block are its rendezvous flag words."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, gpu: Gpu, group, nbytes: int):
+        dist = _dist()
+        self.gpu, self.group = gpu, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.local = gpu.peer_alloc(self.FLAG_BYTES + int(nbytes))
+        self.nbytes = self.FLAG_BYTES + int(nbytes)
+        self.base = [self.local.ptr] * self.world
+        self.epoch = 0
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, gpu.peer_export(self.local.ptr), group=group)
+            self.base = [self.local.ptr if q == self.rank else gpu.peer_import(handles[q]) for q in range(self.world)]
+            dist.barrier(group=group)  # every block exists, is zeroed and is mapped everywhere before anyone writes
+
+    def addr(self, q: int, offset: int) -> int:
+        """Address, in this process, of byte `offset` of rank q's data area."""
+        return self.base[q] + self.FLAG_BYTES + offset
+
+    def view(self, offset: int, shape, dtype: str) -> Tensor:
+        """Typed view of this rank's own data area."""
+        return type(self.local)(self.local.buf, self.FLAG_BYTES + offset, tuple(shape), dtype)
+
+    def sync(self, mode: int = 0):
+        """Rendezvous of all ranks on the device (bounded wait; a rank that never arrives surfaces at wait())."""
+        self.epoch += 1
+        self.gpu.peer_sync_native(self.base, self.rank, self.world, self.epoch, mode)
+
+    def close(self):
+        if self.base is None:
+            return
+        self.gpu.wait()
+        if self.world > 1:
+            _dist().barrier(group=self.group)  # nobody unmaps or frees while a peer may still store into it
+        for q, ptr in enumerate(self.base):
+            if q != self.rank:
+                self.gpu.peer_unmap(ptr)
+        self.gpu.peer_free(self.local.ptr)
+        self.base = None
 
 
 class TokenShardedLinear:
@@ -129,10 +197,10 @@ class RowParallelLinear:
     def __init__(self, gpu: Gpu, group, codes, scales, bias, M: int, *, block: int = 128, swiglu_in: bool = False,
                  out_dtype: str = "bf16", reduce: str = "int32", scatter: bool = False):
         dist = _dist()
-        if reduce not in ("int32", "f32", "bf16"):
+        if reduce not in ("int32", "f32", "bf16", "push", "push_bf16"):
             raise ValueError(f"reduce={reduce!r}")
-        if scatter and reduce != "int32":
-            raise ValueError("scatter=True is implemented for the exact (int32) reduction")
+        if scatter and reduce not in ("int32", "push", "push_bf16"):
+            raise ValueError("scatter=True is implemented for the int32 reduction and the push variants")
         self.group, self.reduce, self.scatter = group, reduce, scatter
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         N, K = codes.shape
@@ -145,6 +213,17 @@ class RowParallelLinear:
         self.m_pad = ops.pad_rows(M)
         self.a8 = gpu.empty((self.m_pad, k1 - k0), "i8")
         self.sa = gpu.empty((self.m_pad,), "f32")
+        self.push = reduce.startswith("push")
+        if self.push:
+            self.stage_dtype = "i32" if reduce == "push" else "bf16"
+            self.rows, self.slot_bytes, self.stage_bytes, out_off, total = push_layout(
+                self.m_pad, int(N), self.world, self.stage_dtype, None if scatter else out_dtype)
+            self.r0 = self.rank * self.rows
+            self.block_mem = PeerBlock(gpu, group, total)
+            self.out_offset, self.calls = out_off, 0
+            self.out = (gpu.empty((self.rows, int(N)), out_dtype) if scatter
+                        else self.block_mem.view(out_off, (self.m_pad, int(N)), out_dtype))
+            return
         self.out = gpu.empty((self.m_pad, int(N)), out_dtype)
         self.partial = gpu.empty((self.m_pad, int(N)), {"int32": "i32", "f32": "f32", "bf16": "bf16"}[reduce])
         if scatter:  # every rank keeps only its M / p rows of the result: half the traffic of an all-reduce
@@ -165,6 +244,8 @@ class RowParallelLinear:
             dist.all_reduce(self.sa.torch(), op=dist.ReduceOp.MAX, group=self.group)
         gpu.rot_q8_given_amax_native(x_local, stride, self.a8, self.sa, M, D, self.block, mode)
         # (4)-(6)
+        if self.push:
+            return self._push(gpu, wt)
         if self.reduce == "int32":
             ops.gemm(gpu, self.a8, wt, self.partial, M, sa=self.sa, tile=(128, 32, 4))  # i32 output: raw accumulators
             if self.scatter:
@@ -190,6 +271,29 @@ class RowParallelLinear:
             return self.partial
         self.out.torch().copy_(self.partial.torch())
         return self.out
+
+
+    def _push(self, gpu: Gpu, wt: ops.QWeight) -> Tensor:
+        mem, N = self.block_mem, wt.N
+        buf = (self.calls % 2) * self.stage_bytes  # calls alternate between the two staging buffers
+        self.calls += 1
+        # this rank's slot in every owner's staging buffer
+        slots = [mem.addr(o, buf + self.rank * self.slot_bytes) for o in range(self.world)]
+        gpu.gemm_push_native(self.a8, wt.K, wt.w, wt.w_stride, wt.sw, self.sa, slots, self.rows, self.stage_dtype, N,
+                             self.m_pad, N, wt.K)
+        mem.sync()  # every rank's partials of my rows have landed
+        esize = 4 if self.stage_dtype == "i32" else 2
+        outs = [self.out.ptr] if self.scatter else [mem.addr(q, self.out_offset) for q in range(self.world)]
+        gpu.reduce_dequant_native(mem.addr(self.rank, buf), self.slot_bytes // esize, N, self.stage_dtype, self.world,
+                                  self.sa.ptr + 4 * self.r0, wt.sw, self.bias, outs, self.out.dtype, N, self.rows, N,
+                                  row0=0 if self.scatter else self.r0)
+        if not self.scatter:
+            mem.sync()  # every rank's finished rows have landed in my output
+        return self.out
+
+    def close(self):
+        if self.push:
+            self.block_mem.close()
 
 
 class TensorParallelBlock:

@@ -137,6 +137,52 @@ H3B_API int h3b_gemm_w8a8_gated(h3b_ctx *ctx, const int8_t *A, int64_t a_stride,
                                 const void *lora_T, int64_t t_stride, const void *lora_B, int64_t b_stride, int R,
                                 const int32_t *lora_ranges);
 
+/* ---- Row-parallel (K-sharded) layers over the GPUs of one node, data path without a communication library --------
+ * No counterpart in the reference (single GPU). One process and one context per GPU. Every GPU computes a partial
+ * product of ALL M rows over its K shard; GPU o owns rows [o * rows_per_gpu, (o + 1) * rows_per_gpu) of the result.
+ * h3b_gemm_w8a8_push stores each finished tile of the partial product straight into the owner's staging memory
+ * (plain stores through a CUDA IPC peer mapping, overlapping the rest of the product); after h3b_peer_sync the owner
+ * runs h3b_reduce_dequant over its rows, which sums the slots, applies the epilogue and can store the finished rows
+ * into every GPU's output (an all-gather by peer stores; a second h3b_peer_sync then makes them readable everywhere).
+ *
+ *   h3b_peer_alloc    zero-filled device memory that can be shared (cudaMalloc); NULL on failure. Setup only.
+ *   h3b_peer_export   64-byte IPC handle of a h3b_peer_alloc'd block, to be sent to the other processes
+ *   h3b_peer_import   maps another process's block into this one (peer access over NVLink is enabled on first use);
+ *                     returns the local address of the mapping, NULL on failure. Not for a handle of this process.
+ *   h3b_peer_unmap / h3b_peer_free   undo import / alloc
+ *   h3b_peer_sync     flags[q] is (this process's mapping of) GPU q's array of `world` 32-bit words, zero at start.
+ *                     mode 0: store `epoch` into word `rank` of every array, then wait until every word of this
+ *                     GPU's own array has reached `epoch`; mode 1: only the stores; mode 2: only the wait. Epochs
+ *                     must grow from call to call (1, 2, ...). The wait is bounded (about a second); if it runs out
+ *                     the kernel returns and the next h3b_wait fails with a message - the device is not left hanging.
+ *                     Every rank must make the same sequence of calls; the kernels of different ranks run on
+ *                     different GPUs (never use mode 0 between contexts that share one GPU).
+ *   h3b_gemm_w8a8_push  slots[o] = where this GPU's partial of owner o's rows goes: [rows_per_gpu][stage_stride] of
+ *                     stage_dtype inside o's staging block (this GPU's slot there). stage_dtype H3B_I32: raw int32
+ *                     accumulators (sw, sa unused; the sum over GPUs is exact, the result bit-identical to one GPU);
+ *                     H3B_BF16: float(acc) * sa[m] * sw[n] rounded to bf16 (half the traffic; 1e-3-level agreement).
+ *                     M = world * rows_per_gpu, rows_per_gpu % 128 == 0, N % 32 == 0. sa holds the WHOLE-row scales
+ *                     (h3b_rot_amax, MAX over the GPUs, h3b_rot_q8_given_amax).
+ *   h3b_reduce_dequant  stage: this GPU's staging block, `world` slots slot_stride elements apart, each
+ *                     [rows][stage_stride]. int32: out = c_dtype(float(sum) * sa[m] * sw[n] + bias[n]), the operation
+ *                     order of h3b_gemm_w8a8's epilogue; bf16: out = c_dtype(fp32 sum in slot order + bias[n]). The
+ *                     rows are stored at rows row0 .. row0 + rows - 1 of each of the n_out buffers outs[i]
+ *                     ([..][c_stride] of c_dtype; local or peer-mapped). sa points at the owner's first row.
+ * Staging is reused safely when callers alternate between two staging blocks from one layer call to the next: a GPU
+ * passes the rendezvous of call c + 1 only after every owner has finished reading the block of call c. */
+H3B_API void *h3b_peer_alloc(h3b_ctx *ctx, uint64_t bytes);
+H3B_API int h3b_peer_free(h3b_ctx *ctx, void *ptr);
+H3B_API int h3b_peer_export(h3b_ctx *ctx, void *ptr, unsigned char handle[64]);
+H3B_API void *h3b_peer_import(h3b_ctx *ctx, const unsigned char handle[64]);
+H3B_API int h3b_peer_unmap(h3b_ctx *ctx, void *ptr);
+H3B_API int h3b_peer_sync(h3b_ctx *ctx, void *const *flags, int rank, int world, uint32_t epoch, int mode);
+H3B_API int h3b_gemm_w8a8_push(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
+                               const float *sw, const float *sa, void *const *slots, int world, int rows_per_gpu,
+                               int stage_dtype, int64_t stage_stride, int M, int N, int K);
+H3B_API int h3b_reduce_dequant(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride,
+                               int stage_dtype, int world, const float *sa, const float *sw, const float *bias,
+                               void *const *outs, int n_out, int c_dtype, int64_t c_stride, int rows, int N, int row0);
+
 /* The product with a LoRA term for callers that cannot allocate device memory. It has no counterpart in the
  * reference (whose Scratch object, h3metal/ops.py:37-47, simply grows a buffer on demand).
  *

@@ -1,5 +1,7 @@
 """A host-only stand-in for h3metal_b200.gpu.Gpu: holds NumPy arrays and records native calls. Lets the CPU tests
 exercise the launchers' host logic (padding, strides, the two-step LoRA sequence, error behaviour) without a GPU."""
+import os
+
 import numpy as np
 
 from h3metal_b200 import gpu as gpu_mod
@@ -138,3 +140,99 @@ class OracleBackedGpu(RecordingGpu):
         v = gemm_ref.epilogue_q8(self._rows(acc, M, N, acc_stride, "i32"), sa.numpy().reshape(-1)[:M],
                                  sw.numpy().reshape(-1)[:N], bias.numpy().reshape(-1)[:N] if bias is not None else None)
         self._rows(out, M, N, c_stride, out.dtype)[...] = gemm_ref.store_as(v, out.dtype)
+
+
+class SharedPeerGpu(OracleBackedGpu):
+    """Adds the peer-memory natives on files mapped by every rank, so that gloo ranks (processes) can play the GPUs of
+    a row-parallel layer: a "device address" is the address of the mapping in this process, exactly as a CUDA IPC
+    mapping has a different address in every process. The rendezvous is a gloo barrier."""
+
+    def __init__(self, group=None, tile_n=None):
+        super().__init__(tile_n)
+        self.group = group
+        self._regions = []  # (address, nbytes, uint8 array, path or None)
+
+    def _register(self, arr, path=None):
+        self._regions.append((arr.ctypes.data, arr.nbytes, arr, path))
+        return arr.ctypes.data
+
+    def _bytes(self, ptr, nbytes):
+        for start, size, arr, _ in self._regions:
+            if start <= ptr and ptr + nbytes <= start + size:
+                return arr[ptr - start:ptr - start + nbytes]
+        raise KeyError(f"address {ptr:#x} (+{nbytes}) is not in a known buffer")
+
+    def empty(self, shape, dtype="f32"):
+        t = super().empty(shape, dtype)
+        self._register(t.buf.arr)
+        return t
+
+    def wait(self):
+        return 0.0
+
+    def peer_alloc(self, nbytes):
+        import tempfile
+        fd, path = tempfile.mkstemp(prefix="h3b_peer_")
+        os.close(fd)
+        arr = np.memmap(path, dtype=np.uint8, mode="w+", shape=(int(nbytes),))
+        self._register(arr, path)
+        return HostTensor(HostBuffer(arr), 0, (int(nbytes),), "u8")
+
+    def peer_export(self, ptr):
+        return next(path for start, _, _, path in self._regions if start == ptr).encode()
+
+    def peer_import(self, handle):
+        arr = np.memmap(bytes(handle).decode(), dtype=np.uint8, mode="r+")
+        return self._register(arr)
+
+    def peer_unmap(self, ptr):
+        self._regions = [r for r in self._regions if r[0] != ptr]
+
+    def peer_free(self, ptr):
+        path = next(path for start, _, _, path in self._regions if start == ptr)
+        self.peer_unmap(ptr)
+        os.unlink(path)
+
+    def peer_sync_native(self, flags, rank, world, epoch, mode=0):
+        import torch.distributed as dist
+        assert mode == 0 and len(flags) == world
+        for _, _, arr, path in self._regions:
+            if path is not None or isinstance(arr, np.memmap):
+                arr.flush()
+        dist.barrier(group=self.group)
+
+    def gemm_push_native(self, a, a_stride, w, w_stride, sw, sa, slots, rows_per_gpu, stage_dtype, stage_stride, M, N, K):
+        from oracle import gemm_ref
+        assert M == rows_per_gpu * len(slots) and stage_stride == N
+        acc = gemm_ref.int32_product(self._rows(a, M, K, a_stride, "i8"), self._rows(w, N, K, w_stride, "i8"))
+        for o, slot in enumerate(slots):
+            part = acc[o * rows_per_gpu:(o + 1) * rows_per_gpu]
+            if stage_dtype == "i32":
+                self._bytes(slot, part.size * 4).view(np.int32).reshape(part.shape)[...] = part
+            else:
+                v = gemm_ref.epilogue_q8(part, sa.numpy().reshape(-1)[o * rows_per_gpu:(o + 1) * rows_per_gpu],
+                                         sw.numpy().reshape(-1)[:N], None)
+                self._bytes(slot, part.size * 2).view(np.uint16).reshape(part.shape)[...] = gemm_ref.store_as(v, "bf16")
+
+    def reduce_dequant_native(self, stage_ptr, slot_stride, stage_stride, stage_dtype, world, sa_ptr, sw, bias, outs,
+                              out_dtype, c_stride, rows, N, row0=0):
+        from oracle import bf16_bits_to_f32, gemm_ref
+        assert stage_stride == N and c_stride == N and slot_stride == rows * N
+        esize = 4 if stage_dtype == "i32" else 2
+        stage = self._bytes(stage_ptr, world * rows * N * esize)
+        b = bias.numpy().reshape(-1)[:N] if bias is not None else None
+        if stage_dtype == "i32":
+            acc = stage.view(np.int32).reshape(world, rows, N).sum(axis=0, dtype=np.int32)
+            v = gemm_ref.epilogue_q8(acc, self._bytes(sa_ptr, rows * 4).view(np.float32), sw.numpy().reshape(-1)[:N], b)
+        else:
+            parts = bf16_bits_to_f32(stage.view(np.uint16).reshape(world, rows, N))
+            v = np.zeros((rows, N), np.float32)
+            for s in range(world):
+                v = (v + parts[s]).astype(np.float32)
+            if b is not None:
+                v = (v + b[None, :]).astype(np.float32)
+        bits = gemm_ref.store_as(v, out_dtype)
+        osize = gpu_mod._SIZE[out_dtype]
+        for o in outs:
+            dst = self._bytes(o + row0 * N * osize, rows * N * osize)
+            dst.view(gpu_mod._NP[out_dtype]).reshape(rows, N)[...] = bits

@@ -1,5 +1,6 @@
-"""Two GPUs, one process each, NCCL: the sharded layers of h3metal_b200.parallel against the single-GPU result.
-Skipped on a box with one GPU (the CPU suite covers the orchestration with gloo)."""
+"""One process per GPU, NCCL for the plumbing: the sharded layers of h3metal_b200.parallel against the single-GPU
+result, including the row-parallel variants that push their partials through peer-mapped memory. The two-GPU case is
+skipped on a box with one GPU (the CPU suite covers the orchestration with gloo); the one-rank case runs anywhere."""
 import os
 import socket
 import subprocess
@@ -25,7 +26,7 @@ rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 g = Gpu(device=rank)
-M, D, F, B = 384, 1024, 2048, 128
+M, D, F, B = 512, 1024, 2048, 128
 rng = np.random.default_rng(5)
 x = oracle.bf16_round_bits((rng.standard_normal((M, D)) * 2).astype(np.float32))
 w_up = rng.integers(-127, 128, size=(2 * F, D), dtype=np.int8); s_up = rng.uniform(1e-3, 2e-3, size=2 * F).astype(np.float32)
@@ -51,23 +52,38 @@ assert np.array_equal(down.sa.numpy(), sab.numpy()), "whole-row scales"
 half = F // world
 assert np.array_equal(down.a8.numpy(), a8b.numpy()[:, rank * half:(rank + 1) * half]), "K-shard codes"
 assert np.array_equal(y.numpy(), y1.numpy()), "row-parallel output"
+r0 = rank * (M // world)
+for reduce, scatter in (("int32", True), ("push", False), ("push", True), ("push_bf16", False), ("push_bf16", True)):
+    layer = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=B, swiglu_in=True, reduce=reduce, scatter=scatter)
+    for call in range(3):  # staging buffers alternate and are reused
+        yp = layer(h_local)
+        g.wait()
+        want = y1.numpy()[r0:r0 + M // world] if scatter else y1.numpy()
+        if reduce == "push_bf16":
+            a, b = oracle.bf16_bits_to_f32(yp.numpy()), oracle.bf16_bits_to_f32(want)
+            rel = np.linalg.norm(a - b) / np.linalg.norm(b)
+            assert rel < 5e-3, (reduce, scatter, call, rel)
+        else:
+            assert np.array_equal(yp.numpy(), want), (reduce, scatter, call)
+    layer.close()
 dist.barrier(); dist.destroy_process_group()
 print(f"rank {rank} ok")
 '''
 
 
-def test_two_gpus_match_one_gpu_bit_for_bit(tmp_path):
+@pytest.mark.parametrize("world", [1, 2])
+def test_sharded_layers_match_one_gpu_bit_for_bit(tmp_path, world):
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     procs = []
-    for rank in range(2):
-        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+    for rank in range(world):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                    MASTER_PORT=str(port), H3B_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))

@@ -28,6 +28,12 @@ def test_shard_plans():
     assert parallel.column_slices(2 * 1024, [1024, 1024], 0, 2) == [(0, 512), (1024, 1536)]
     with pytest.raises(ValueError):
         parallel.column_slices(100, [60, 30], 0, 2)
+    # peer block of a push layer: two staging buffers of `world` slots, then the gathered output
+    assert parallel.push_layout(1024, 512, 4, "i32", "bf16") == (256, 256 * 512 * 4, 4 * 256 * 512 * 4, 2 * 1024 * 512 * 4,
+                                                                  2 * 1024 * 512 * 4 + 1024 * 512 * 2)
+    assert parallel.push_layout(1024, 512, 4, "bf16", None)[4] == 2 * 1024 * 512 * 2
+    with pytest.raises(ValueError):
+        parallel.push_layout(384, 512, 2, "i32", None)  # 192 rows per rank: not whole 128-row tiles
     a = np.arange(12).reshape(6, 2)
     assert parallel.take_rows(a, [(0, 1), (4, 6)]).tolist() == [[0, 1], [8, 9], [10, 11]]
 
@@ -57,8 +63,8 @@ def _worker(rank, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=WORLD)
     try:
-        from tests.fakes import OracleBackedGpu
-        g = OracleBackedGpu()
+        from tests.fakes import SharedPeerGpu
+        g = SharedPeerGpu()
         x, (w_up, s_up, b_up), (w_dn, s_dn, b_dn) = _inputs()
         up = parallel.ColumnParallelLinear(g, None, w_up, s_up, b_up, M, block=BLOCK, splits=[F, F])
         down = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True)
@@ -68,12 +74,20 @@ def _worker(rank, port, results):
         y_rows = down_rs(h_local)
         down_f32 = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True, reduce="f32")
         y_fast = down_f32(h_local)
+        pushed = {}
+        for reduce, scatter in (("push", False), ("push", True), ("push_bf16", False), ("push_bf16", True)):
+            layer = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True, reduce=reduce,
+                                               scatter=scatter)
+            outs = [layer(h_local).numpy().copy() for _ in range(3)]  # three calls: both staging buffers, reused
+            assert all(np.array_equal(o, outs[0]) for o in outs)
+            pushed[(reduce, scatter)] = outs[0]
+            layer.close()
         tok = parallel.TokenShardedLinear(g, None, parallel.ops.QWeight("q8", g.upload(w_up), g.upload(s_up), 2 * F, D,
                                                                          bias=g.upload(b_up)), M, block=BLOCK)
         h_tok = tok(g.upload(x[tok.m0:tok.m0 + tok.rows], "bf16"))
         results[rank] = dict(slices=up.slices, h_local=h_local.numpy().copy(), a8=down.a8.numpy().copy(),
                              sa=down.sa.numpy().copy(), y=y.numpy().copy(), y_rows=(down_rs.r0, y_rows.numpy().copy()), y_fast=y_fast.numpy().copy(),
-                             tok=(tok.m0, tok.rows, h_tok.numpy().copy()))
+                             tok=(tok.m0, tok.rows, h_tok.numpy().copy()), pushed=pushed)
     finally:
         dist.destroy_process_group()
 
@@ -102,6 +116,14 @@ def test_two_ranks_reproduce_one_rank_bit_for_bit():
         got = oracle.bf16_bits_to_f32(r["y_fast"]).astype(np.float64)
         want = oracle.bf16_bits_to_f32(y).astype(np.float64)
         assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
+        # push variants: partials through (here: file-backed) peer memory; exact for int32 staging
+        for (reduce, scatter), got in r["pushed"].items():
+            want_rows = y[r0:r0 + M // WORLD] if scatter else y
+            if reduce == "push":
+                assert np.array_equal(got, want_rows), (reduce, scatter)
+            else:
+                a, b = oracle.bf16_bits_to_f32(got).astype(np.float64), oracle.bf16_bits_to_f32(want_rows).astype(np.float64)
+                assert np.linalg.norm(a - b) / np.linalg.norm(b) <= 5e-3, (reduce, scatter)
         # token-sharded: rows of the full result
         m0, rows, h_tok = r["tok"]
         assert (m0, rows) == (rank * M // WORLD, M // WORLD) and np.array_equal(h_tok, h[m0:m0 + rows])
