@@ -491,6 +491,9 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
     band = static_cast<int>(budget / (static_cast<long long>(tile_m) * K));
     if (band < (pair ? 2 : 4)) band = pair ? 2 : 4;
   }
+  // push: the tiles in flight at any moment should span every owner's rows, so that no GPU's incoming links
+  // become the bottleneck while others idle: one band over all rows (A's K shard is small enough for L2)
+  if (push && static_cast<long long>(M) * K <= (64LL << 20)) band = m_tiles;
   if (band > m_tiles) band = m_tiles;
   g.band = band;
   const long long tiles = static_cast<long long>(m_tiles) * n_tiles;

@@ -22,7 +22,9 @@ constexpr int kTmemCols = 512;
 constexpr int kLowBase = 256;       // first TMEM column of the LoRA accumulators
 constexpr int kThreads = 192;
 constexpr int kBarrierBytes = 256;
-constexpr int kPushBytes = 4 * 4096;  // row-parallel push: a 32 x 32-word transposition buffer per epilogue warp
+// Row-parallel push: the transposition buffers of the four epilogue warps. int32 partials need 8 KB per warp and use
+// the (then idle) column staging as well; bf16 partials need 4 KB per warp behind the column staging.
+__host__ __device__ constexpr int push_bytes(int bn) { return 32768 - 16 * bn * 4 > 16384 ? 32768 - 16 * bn * 4 : 16384; }
 
 __host__ __device__ constexpr int stage_bytes(int bn) { return kABytes + bn * kBKBytes; }
 __host__ __device__ constexpr int lora_bytes(int bn, int R) { return (R / kLoraChunk) * (kLoraTBytes + bn * kLoraChunk * 2); }
@@ -181,48 +183,59 @@ __device__ __forceinline__ void finish_chunk(const GemmLaunch &g, const uint32_t
   else store_segment(static_cast<float *>(g.c) + off, v, n_valid, vec_ok);
 }
 
-// Row-parallel push: the warp's 32 rows x 32 columns [n, n + 32) of this GPU's partial product go to the staging
-// slot of the rows' owner, which may be another GPU (plain stores through a peer mapping). A lane holds one ROW of
-// the chunk, so a direct store would touch 32 rows with 16 bytes each; over NVLink that is 32 small packets. The chunk
-// is therefore transposed through the warp's 4 KB of shared memory first: afterwards eight (int32) or four (bf16)
-// neighbouring lanes hold one row's 128 or 64 contiguous bytes and every store instruction writes whole lines.
-// `xpose` is the warp's own buffer; 16-byte piece k of row r sits at piece k ^ (r & 7) so that both the row-wise
-// writes and the line-wise reads spread over the banks. dst_rows points at row 0 of the tile's 128 rows in the slot.
-__device__ __forceinline__ void push_chunk(const GemmLaunch &g, const uint32_t (&acc)[32], int quarter, int lane, int n,
-                                           float sa_m, const float *sw_s, const float *bias_s, uint4 *xpose,
-                                           uint8_t *dst_rows) {
-  if (n >= g.N) return;  // a column tile hanging over N (N is a multiple of 32: chunks are whole or absent)
-  const uint32_t no_low[32] = {};
-  __syncwarp();
+// Row-parallel push: the warp's 32 rows x 64 columns [n, n + 64) of this GPU's partial product (two TMEM chunks)
+// go to the staging slot of the rows' owner, which may be another GPU (plain stores through a peer mapping). A lane
+// holds one ROW of a chunk, so a direct store would touch 32 rows with 16 bytes each; over NVLink that is 32 small
+// packets. The two chunks are therefore transposed through shared memory first: afterwards sixteen (int32) or
+// eight (bf16) neighbouring lanes hold one row's 256 or 128 contiguous bytes and every store instruction writes
+// whole lines. `xpose` is the warp's own buffer, [32 rows][16 or 8 pieces of 16 bytes]; piece p of row r sits at
+// p ^ (r & 7), so that both the row-wise writes and the line-wise reads spread over the banks.
+//
+// push_stage: chunk `half` (0 or 1) of the pair into the buffer. push_flush: the buffer's first `cols` (32 or 64)
+// columns to dst_rows (row 0 of the tile's 128 rows in the slot) at column n.
+__device__ __forceinline__ void push_stage(const GemmLaunch &g, const uint32_t (&acc)[32], int half, int lane, float sa_m,
+                                           const float *sw_s, const float *bias_s, uint4 *xpose) {
   if (g.c_dtype == kDtypeI32) {
 #pragma unroll
     for (int k = 0; k < 8; ++k)
-      xpose[lane * 8 + (k ^ (lane & 7))] = make_uint4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
-    __syncwarp();
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {  // four rows per instruction, eight lanes (128 bytes) per row
-      const int r = 4 * i + (lane >> 3), k = lane & 7;
-      const uint4 q = xpose[r * 8 + (k ^ (r & 7))];
-      uint8_t *row = dst_rows + static_cast<size_t>(quarter * 32 + r) * g.c_stride * 4;
-      *reinterpret_cast<uint4 *>(row + static_cast<size_t>(n) * 4 + k * 16) = q;
-    }
+      xpose[lane * 16 + ((half * 8 + k) ^ (lane & 7))] = make_uint4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]);
   } else {  // bf16 partials: float(acc) * sa * sw, no bias (the owner adds it once)
+    const uint32_t no_low[32] = {};
     float v[32];
     dequant32(g, acc, no_low, false, sa_m, sw_s, bias_s, v);
     uint32_t w[32];
     Packed<__nv_bfloat16>::pack(v, w);
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-      xpose[lane * 8 + (k ^ (lane & 7))] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
-    __syncwarp();
+      xpose[lane * 8 + ((half * 4 + k) ^ (lane & 7))] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+  }
+}
+
+__device__ __forceinline__ void push_flush(const GemmLaunch &g, int quarter, int lane, int n, int cols, const uint4 *xpose,
+                                           uint8_t *dst_rows) {
+  __syncwarp();
+  if (g.c_dtype == kDtypeI32) {
+    const int p = lane & 15;
+    if (4 * p < cols) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {  // eight rows per instruction, four lanes (64 bytes) per row
-      const int r = 8 * i + (lane >> 2), k = lane & 3;
-      const uint4 q = xpose[r * 8 + (k ^ (r & 7))];
-      uint8_t *row = dst_rows + static_cast<size_t>(quarter * 32 + r) * g.c_stride * 2;
-      *reinterpret_cast<uint4 *>(row + static_cast<size_t>(n) * 2 + k * 16) = q;
+      for (int i = 0; i < 16; ++i) {  // two rows per instruction, sixteen lanes (256 bytes) per row
+        const int r = 2 * i + (lane >> 4);
+        uint8_t *row = dst_rows + static_cast<size_t>(quarter * 32 + r) * g.c_stride * 4;
+        *reinterpret_cast<uint4 *>(row + static_cast<size_t>(n) * 4 + p * 16) = xpose[r * 16 + (p ^ (r & 7))];
+      }
+    }
+  } else {
+    const int p = lane & 7;
+    if (8 * p < cols) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {  // four rows per instruction, eight lanes (128 bytes) per row
+        const int r = 4 * i + (lane >> 3);
+        uint8_t *row = dst_rows + static_cast<size_t>(quarter * 32 + r) * g.c_stride * 2;
+        *reinterpret_cast<uint4 *>(row + static_cast<size_t>(n) * 2 + p * 16) = xpose[r * 8 + (p ^ (r & 7))];
+      }
     }
   }
+  __syncwarp();  // the buffer may be overwritten by the next pair
 }
 
 // Stages the column scales and biases of columns [n0, n0 + bn) in a warp's own slice of shared memory.

@@ -60,8 +60,10 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
   volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(base_ptr + bars_off + 176);
   volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + bars_off + 180);
   float *col_stage = reinterpret_cast<float *>(base_ptr + bars_off + kBarrierBytes);  // [EPI_WARPS][2][BN]: sw, bias
-  // PUSH: 4 KB per epilogue warp behind the column staging, for the transposition of outgoing chunks
-  uint4 *xpose_all = reinterpret_cast<uint4 *>(base_ptr + bars_off + kBarrierBytes + 16 * BN * sizeof(float));
+  // PUSH: transposition buffers of outgoing chunk pairs. int32 partials: 8 KB per epilogue warp from the start of the
+  // column staging (which raw accumulators do not use); bf16 partials: 4 KB per warp behind the column staging.
+  uint4 *xpose_raw = reinterpret_cast<uint4 *>(col_stage);
+  uint4 *xpose_bf16 = reinterpret_cast<uint4 *>(base_ptr + bars_off + kBarrierBytes + 16 * BN * sizeof(float));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (g.M + kBM - 1) / kBM, n_tiles = (g.N + BN - 1) / BN;
@@ -233,12 +235,12 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
       uint8_t *push_rows = nullptr;  // PUSH: row 0 of this tile in the owner's staging slot
       if constexpr (PUSH) {
         const int owner = m0 / g.peer_rows;
-        xpose = xpose_all + (warp - 2) * 256;
+        xpose = raw ? xpose_raw + (warp - 2) * 512 : xpose_bf16 + (warp - 2) * 256;
         push_rows = static_cast<uint8_t *>(g.peer_c[owner]) +
                     static_cast<size_t>(m0 - owner * g.peer_rows) * g.c_stride * (raw ? 4 : 2);
       }
       auto finish = [&](const uint32_t (&acc)[32], const uint32_t (&low)[32], int c) {
-        if constexpr (PUSH) push_chunk(g, acc, quarter, lane, n0 + c * 32, sa_m, sw_s + c * 32, bias_s + c * 32, xpose, push_rows);
+        if constexpr (PUSH) push_stage(g, acc, (c - c_begin) & 1, lane, sa_m, sw_s + c * 32, bias_s + c * 32, xpose);
         else finish_chunk(g, acc, low, LORA && has_low, m, n0 + c * 32, sa_m, sw_s + c * 32, bias_s + c * 32, vec_ok);
       };
       ok = mbar_wait(acc_full_bar(as), aph, cta_abort, g.status, kStatusEpilogueTimeout);
@@ -263,6 +265,11 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
           if (c + 2 < c_end) fetch(c + 2, acc_a, low_a);
           finish(acc_b, low_b, c + 1);
         }
+        if constexpr (PUSH) {  // the pair's columns, as far as they lie inside N (a multiple of 32)
+          const int n = n0 + c * 32;
+          const int have = c + 1 < c_end ? 64 : 32;
+          if (n < g.N) push_flush(g, quarter, lane, n, min(have, g.N - n), xpose, push_rows);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -281,7 +288,7 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
 
 template <int BN, int ACC_STAGES, bool LORA, int EPI, bool PUSH = false>
 cudaError_t launch_one(const GemmLaunch &g, int stages, cudaStream_t stream) {
-  const size_t smem = gemm_smem_bytes(BN, LORA ? g.R : 0, stages) + (PUSH ? kPushBytes : 0);
+  const size_t smem = gemm_smem_bytes(BN, LORA ? g.R : 0, stages) + (PUSH ? push_bytes(BN) : 0);
   gemm_w8a8_kernel<BN, ACC_STAGES, LORA, EPI, PUSH><<<g.grid, 64 + 32 * EPI, smem, stream>>>(g, stages);
   return cudaGetLastError();
 }
@@ -303,7 +310,7 @@ size_t gemm_smem_bytes(int bn, int R, int stages) {
 
 int gemm_pick_stages(int bn, int R, size_t smem_optin, bool push) {
   for (int s = kMaxStages; s >= 2; --s) {
-    const size_t need = gemm_smem_bytes(bn, R, s) + (push ? kPushBytes : 0);
+    const size_t need = gemm_smem_bytes(bn, R, s) + (push ? push_bytes(bn) : 0);
     if (need != 0 && need <= smem_optin) return s;
   }
   return 0;
