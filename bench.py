@@ -220,6 +220,8 @@ def run_ours(args, cfg, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     gpu = Gpu(device=local)
+    if args.overlap:
+        gpu.set_launch_overlap(True)
     dev = gpu.torch_device
     if args.parallel == "tp":
         return run_tensor_parallel(args, cfg, rank, world, gpu)
@@ -510,6 +512,8 @@ def main():
                          "push_bf16 = the same with bf16 partials)")
     ap.add_argument("--scatter", action="store_true",
                     help="tp: reduce-scatter instead of all-reduce (every rank finishes its M / N_gpus rows)")
+    ap.add_argument("--overlap", action="store_true",
+                    help="launch the kernels with programmatic dependent launch (off by default: slower on this block)")
     ap.add_argument("--library-int8-probe", action="store_true",
                     help="time the vendor library's int8 and bf16 GEMMs on this GPU (a yardstick; runs nothing of the path)")
     ap.add_argument("--whole-block", action="store_true",

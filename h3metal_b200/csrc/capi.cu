@@ -82,7 +82,8 @@ struct h3b_ctx {
   int *status_host = nullptr;  // pinned copy read at wait
   EncodeTiledFn encode = nullptr;
   std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
-  int tile_n_override = 0, band_override = 0, pair_mode = 0, rot_threads = 0, rot_stages = 0;
+  int tile_n_override = 0, band_override = 0, pair_mode = 0, rot_threads = 0, rot_stages = 0, rot_chunk = 0;
+  int overlap = 0;  // programmatic dependent launch of the path's two main kernels (h3b_set_launch_overlap)
   int pair_stages = 0, pair_clusters = 0;  // CTA-pair product: ring depth and resident clusters (0 = unavailable)
   uint64_t launches = 0;
   std::string name;
@@ -268,11 +269,19 @@ int h3b_use_own_stream(h3b_ctx *ctx) {
   return 0;
 }
 
-int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target, int tma_stages) {
+int h3b_set_launch_overlap(h3b_ctx *ctx, int on) {
+  if (!ctx) return fail("null context");
+  ctx->overlap = on != 0;
+  return 0;
+}
+
+int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target, int tma_stages, int chunk) {
   if (!ctx) return fail("null context");
   if (tma_stages < -1 || tma_stages > 4) return fail("rot policy: tma_stages must be -1 (off), 0 (automatic) or 1..4");
+  if (chunk != 0 && chunk != 32 && chunk != 64) return fail("rot policy: chunk must be 0 (automatic), 32 or 64");
   ctx->rot_threads = threads_target;
   ctx->rot_stages = tma_stages;
+  ctx->rot_chunk = chunk;
   return 0;
 }
 
@@ -300,7 +309,8 @@ static int rot_enqueue(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_strid
     if (!map) return -1;
     if (ctx->before_launch(&ps)) return -1;
     const cudaError_t e = h3b::launch_rot_q8_tma(*map, x_dtype, out, sa, M, D, block, mode, out_hr, scale_mode, ctx->rot_stages,
-                                                 ctx->prop.multiProcessorCount, ctx->status_dev, ctx->stream);
+                                                 ctx->rot_chunk, ctx->prop.multiProcessorCount, ctx->status_dev,
+                                                 ctx->stream, ctx->overlap != 0 && !ctx->profile);
     return ctx->after_launch("rot_q8 launch", e);
   }
   int target = ctx->rot_threads > 0 ? ctx->rot_threads : 256;
@@ -498,6 +508,7 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
   g.band = band;
   const long long tiles = static_cast<long long>(m_tiles) * n_tiles;
   g.status = ctx->status_dev;
+  g.overlap = (ctx->overlap != 0 && !ctx->profile) ? 1 : 0;
 
   cudaEvent_t ps = nullptr;
   if (ctx->before_launch(&ps)) return -1;

@@ -98,6 +98,10 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
+  // everything above touched only this CTA's shared and tensor memory; from here on global memory is read and
+  // written, which must wait for the kernel before this one in the stream
+  grid_dep_launch();
+  grid_dep_wait();
 
   if (warp == 0) {
     // ---------------------------------------------------------------------------------- TMA producer
@@ -289,8 +293,17 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
 template <int BN, int ACC_STAGES, bool LORA, int EPI, bool PUSH = false>
 cudaError_t launch_one(const GemmLaunch &g, int stages, cudaStream_t stream) {
   const size_t smem = gemm_smem_bytes(BN, LORA ? g.R : 0, stages) + (PUSH ? push_bytes(BN) : 0);
-  gemm_w8a8_kernel<BN, ACC_STAGES, LORA, EPI, PUSH><<<g.grid, 64 + 32 * EPI, smem, stream>>>(g, stages);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(g.grid);
+  cfg.blockDim = dim3(64 + 32 * EPI);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g.overlap ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, gemm_w8a8_kernel<BN, ACC_STAGES, LORA, EPI, PUSH>, g, stages);
 }
 
 template <int BN, int ACC_STAGES, bool LORA, int EPI, bool PUSH = false>

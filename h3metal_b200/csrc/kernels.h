@@ -25,9 +25,10 @@ cudaError_t launch_norm_mod_q8(float *x, long long x_stride, const float *mod, l
 // TMA-fed variant for bf16 / fp16 inputs of up to 16384 channels. `map` describes the input as
 // {64, cols / 64, M} with box {64, D / 64, 1} and 128-byte swizzle (built by the caller).
 bool rot_q8_tma_supported(int x_dtype, int D);
+// chunk_wanted: channels per thread, 32 or 64 (anything else: the default).
 cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, float *sa, int M, int D, int block,
-                              int mode, int out_hr, int scale_mode, int stages_wanted, int sms, int *status,
-                              cudaStream_t stream);
+                              int mode, int out_hr, int scale_mode, int stages_wanted, int chunk_wanted, int sms,
+                              int *status, cudaStream_t stream, bool overlap = false);
 // The norm + modulation front end on the same TMA-fed kernel: fp32 rows of up to 8192 channels, no fused residual
 // update. `map` describes x as {32 floats, D / 32, M} and `map_mod` the modulation table as
 // {32 floats, mod_stride / 32, types}, both with box {32, D / 32, 1} and 128-byte swizzle.
@@ -108,6 +109,7 @@ struct GemmLaunch {
   // bias). peer_rows == 0: no push, `c` is used.
   void *peer_c[kMaxPeers];
   int peer_rows;
+  int overlap;         // host side: launch with programmatic stream serialization (prologue overlaps the previous kernel's tail)
 };
 
 // Shared memory a launch with this tile width and rank needs for `stages` operand stages; 0 if unsupported.

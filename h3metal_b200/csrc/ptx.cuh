@@ -81,6 +81,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it in the
+// stream is still running. grid_dep_wait() blocks until that kernel has completed and its memory is visible: it must
+// come before the first access to global memory. grid_dep_launch() lets the NEXT kernel's CTAs be scheduled as soon as
+// this kernel's CTAs free their resources. Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA ------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

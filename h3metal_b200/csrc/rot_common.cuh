@@ -75,20 +75,21 @@ __device__ __forceinline__ void widen(const RawChunk<float> &r, float (&v)[kChun
 // itself has between math libraries, which is what the one-step-on-1e-4-of-codes allowance of this mode is for.
 __device__ __forceinline__ float silu(float g) { return __fdividef(g, __fadd_rn(1.0f, expf(-g))); }
 
-// In-thread butterfly stages of stride 1, 2, 4, 8, 16, 32 over the chunk's 64 values. Stride 1 pairs the two halves of
-// a float2 and stays scalar; the others combine whole float2 registers: a + b and fma(b, -1, a) = a - b.
-__device__ __forceinline__ void chunk_butterflies(float (&v)[kChunk]) {
+// In-thread butterfly stages of stride 1, 2, ... N / 2 over a thread's N (64 or 32) values. Stride 1 pairs the two
+// halves of a float2 and stays scalar; the others combine whole float2 registers: a + b and fma(b, -1, a) = a - b.
+template <int N>
+__device__ __forceinline__ void chunk_butterflies(float (&v)[N]) {
 #pragma unroll
-  for (int i = 0; i < kChunk; i += 2) {
+  for (int i = 0; i < N; i += 2) {
     const float a = v[i], b = v[i + 1];
     v[i] = __fadd_rn(a, b);
     v[i + 1] = __fsub_rn(a, b);
   }
   const float2 minus_one = make_float2(-1.0f, -1.0f);
 #pragma unroll
-  for (int s = 2; s < kChunk; s <<= 1) {
+  for (int s = 2; s < N; s <<= 1) {
 #pragma unroll
-    for (int i = 0; i < kChunk; i += 2) {
+    for (int i = 0; i < N; i += 2) {
       if ((i & s) == 0) {
         const float2 a = make_float2(v[i], v[i + 1]), b = make_float2(v[i + s], v[i + s + 1]);
         const float2 sum = __fadd2_rn(a, b), dif = __ffma2_rn(b, minus_one, a);
@@ -99,16 +100,16 @@ __device__ __forceinline__ void chunk_butterflies(float (&v)[kChunk]) {
   }
 }
 
-// Stages of stride 64 .. BLOCK/2: the partner value lives in lane ^ (stride / 64). The lower lane keeps v + o, the
+// Stages of stride N .. BLOCK/2: the partner value lives in lane ^ (stride / N). The lower lane keeps v + o, the
 // upper lane o - v; both are o + sign * v with sign = +-1 (the product is exact, so the fma rounds once).
-template <int BLOCK>
-__device__ __forceinline__ void lane_butterflies(float (&v)[kChunk], int lane) {
+template <int BLOCK, int N>
+__device__ __forceinline__ void lane_butterflies(float (&v)[N], int lane) {
 #pragma unroll
-  for (int s = 1; s < BLOCK / kChunk; s <<= 1) {
+  for (int s = 1; s < BLOCK / N; s <<= 1) {
     const float sg = (lane & s) ? -1.0f : 1.0f;
     const float2 sign = make_float2(sg, sg);
 #pragma unroll
-    for (int i = 0; i < kChunk; i += 2) {
+    for (int i = 0; i < N; i += 2) {
       const float2 o = make_float2(__shfl_xor_sync(0xFFFFFFFFu, v[i], s), __shfl_xor_sync(0xFFFFFFFFu, v[i + 1], s));
       const float2 r = __ffma2_rn(make_float2(v[i], v[i + 1]), sign, o);
       v[i] = r.x; v[i + 1] = r.y;

@@ -7,13 +7,15 @@
 // flight without spending registers or load instructions on it, and the warps only compute:
 //   * the input [M][stride] is described to TMA as a 3-D tensor {128 bytes of channels, chunks, M rows}; one
 //     cp.async.bulk.tensor copy brings a whole row into a stage, 128-byte swizzled;
-//   * thread t owns 64 consecutive channels: one 128-byte shared-memory line for 16-bit inputs (eight 16-byte
+//   * thread t owns CH = 64 consecutive channels: one 128-byte shared-memory line for 16-bit inputs (eight 16-byte
 //     loads), two lines for fp32. The swizzle places piece k of line r at column k ^ (r & 7), so the eight threads
-//     of a quarter-warp hit different bank groups although their lines lie 128 (or 256) bytes apart;
+//     of a quarter-warp hit different bank groups although their lines lie 128 (or 256) bytes apart. With CH = 32
+//     (16-bit inputs only) a thread owns half a line: half the registers per thread, so twice the threads per SM
+//     hide the latencies of the arithmetic, at the price of one more cross-lane butterfly stage;
 //   * after the first CTA barrier of a row (the exchange of the row statistic: the sum of squares with the norm
 //     front end, else the row maximum) every thread has finished reading the stage, and thread 0 re-arms it with
 //     the row `stages` rows ahead; no separate "empty" barrier is needed.
-// One warp per 2048 channels; CTAs are persistent over rows m = blockIdx.x, += gridDim.x. Only one thread polls a
+// One warp per 32 CH channels; CTAs are persistent over rows m = blockIdx.x, += gridDim.x. Only one thread polls a
 // stage's barrier; the CTA barrier that follows releases everybody with a uniform go / stop decision. Waits are
 // bounded: on a timeout the CTA sets the context's status word, stops taking rows, waits (bounded) for its copies
 // in flight and returns.
@@ -52,12 +54,15 @@ struct RotTmaArgs {
   float normaliser;
   float eps;
   int scale_mode;      // 0: scale from this row's maximum; 1: only write the maximum to sa; 2: sa holds the maximum to use
+  int overlap;         // host side: launch with programmatic stream serialization
 };
 
-// 64 consecutive values of the thread's chunk `t`, widened to fp32. IN: 0 bf16, 1 fp16 (one line), 2 fp32 (two lines).
-template <int IN>
-__device__ __forceinline__ void read_chunk(const uint8_t *stage, int t, float (&v)[kChunk]) {
+// CH consecutive values of the thread's chunk `t`, widened to fp32. IN: 0 bf16, 1 fp16 (a line, or half a line with
+// CH = 32), 2 fp32 (two lines; CH = 64 only).
+template <int IN, int CH>
+__device__ __forceinline__ void read_chunk(const uint8_t *stage, int t, float (&v)[CH]) {
   if constexpr (IN == 2) {
+    static_assert(CH == 64, "fp32 rows are read 64 channels per thread");
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int line = 2 * t + half;
@@ -71,11 +76,14 @@ __device__ __forceinline__ void read_chunk(const uint8_t *stage, int t, float (&
       }
     }
   } else {
-    const uint8_t *row = stage + t * 128;
-    const int sw = t & 7;
+    constexpr int kPieces = CH / 8;                       // 16-byte pieces per thread: 8 (a whole line) or 4
+    const int line = CH == 64 ? t : t >> 1;
+    const int first = CH == 64 ? 0 : (t & 1) * 4;
+    const uint8_t *row = stage + line * 128;
+    const int sw = line & 7;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const uint4 q = *reinterpret_cast<const uint4 *>(row + ((k ^ sw) << 4));
+    for (int k = 0; k < kPieces; ++k) {
+      const uint4 q = *reinterpret_cast<const uint4 *>(row + (((first + k) ^ sw) << 4));
       const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -101,20 +109,21 @@ __device__ __forceinline__ float sum64(const float (&v)[kChunk], bool squares) {
   return __fadd_rn(__fadd_rn(s[0], s[1]), __fadd_rn(s[2], s[3]));
 }
 
-template <int IN, int BLOCK, int FRONT, bool LN, int OUT>
-__global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__ RotTmaArgs p) {
+template <int IN, int BLOCK, int FRONT, bool LN, int OUT, int CH = kChunk>
+__global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const __grid_constant__ RotTmaArgs p) {
+  static_assert(CH == 64 || (CH == 32 && IN != 2 && FRONT != kNorm), "half-line chunks: 16-bit inputs, no norm front end");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t *base_ptr = smem_raw + (base - raw_addr);
   const uint32_t tail = p.stages * p.stage_bytes;
   const uint32_t bars = base + tail;                                       // full[kMaxStages]
-  float *exchange = reinterpret_cast<float *>(base_ptr + tail + 64);       // [4][8]: row statistics, rotating buffers
-  volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + tail + 192);
+  float *exchange = reinterpret_cast<float *>(base_ptr + tail + 64);       // [4][16]: row statistics, rotating buffers
+  volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + tail + 320);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n_warps = blockDim.x >> 5;
-  const int n_chunks = p.D / kChunk;
+  const int n_chunks = p.D / CH;
   const bool active = tid < n_chunks;
   const float2 norm2 = make_float2(p.normaliser, p.normaliser);
   constexpr int kEsize = IN == 2 ? 4 : 2;
@@ -143,6 +152,9 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
     fence_barrier_init();
   }
   __syncthreads();
+  // so far only this CTA's shared memory was touched; global memory must wait for the previous kernel in the stream
+  grid_dep_launch();
+  grid_dep_wait();
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
       const int m = blockIdx.x + s * gridDim.x;
@@ -159,7 +171,7 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
       const float o = __shfl_xor_sync(0xFFFFFFFFu, v, sft);
       v = is_max ? fmaxf(v, o) : __fadd_rn(v, o);
     }
-    float *buf = exchange + (xbuf++ & 3u) * 8;
+    float *buf = exchange + (xbuf++ & 3u) * 16;
     if (lane == 0) buf[warp] = v;
     __syncthreads();
     float r = buf[0];
@@ -174,18 +186,18 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
     if (!__syncthreads_and(arrived)) break;
 
     const uint8_t *stage = base_ptr + s * p.stage_bytes;
-    float v[kChunk];
+    float v[CH];
     if (active) {
-      read_chunk<IN>(stage, tid, v);
+      read_chunk<IN, CH>(stage, tid, v);
       if (FRONT == kSwiglu) {
-        float g[kChunk];
-        read_chunk<IN>(stage + p.gate_offset, tid, g);
+        float g[CH];
+        read_chunk<IN, CH>(stage + p.gate_offset, tid, g);
 #pragma unroll
-        for (int i = 0; i < kChunk; ++i) v[i] = __fmul_rn(v[i], silu(g[i]));
+        for (int i = 0; i < CH; ++i) v[i] = __fmul_rn(v[i], silu(g[i]));
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
+      for (int i = 0; i < CH; ++i) v[i] = 0.0f;
     }
     bool refilled = false;
     auto refill = [&]() {  // after a CTA barrier that follows the reads: the stage may be overwritten
@@ -203,17 +215,17 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
         const float mean = __fdiv_rn(cta_reduce(sum64(v, false), false), fd);
         if (active) {
 #pragma unroll
-          for (int i = 0; i < kChunk; ++i) v[i] = __fsub_rn(v[i], mean);
+          for (int i = 0; i < CH; ++i) v[i] = __fsub_rn(v[i], mean);
         }
       }
       const float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(cta_reduce(sum64(v, true), false), fd), p.eps));
       if (active) {
-        float sc[kChunk], sh[kChunk];
-        read_chunk<2>(stage + p.gate_offset, tid, sc);
-        read_chunk<2>(stage + 2 * p.gate_offset, tid, sh);
+        float sc[CH], sh[CH];
+        read_chunk<2, CH>(stage + p.gate_offset, tid, sc);
+        read_chunk<2, CH>(stage + 2 * p.gate_offset, tid, sh);
         const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-        for (int i = 0; i < kChunk; i += 2) {
+        for (int i = 0; i < CH; i += 2) {
           float2 x = __fmul2_rn(__fmul2_rn(make_float2(v[i], v[i + 1]), inv2), make_float2(sc[i], sc[i + 1]));
           x = __fadd2_rn(x, make_float2(sh[i], sh[i + 1]));
           v[i] = x.x; v[i + 1] = x.y;
@@ -227,9 +239,9 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
 
     if constexpr (OUT == kOutF32) {
       if (active) {
-        float4 *o = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + static_cast<size_t>(m) * p.D + tid * kChunk);
+        float4 *o = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + static_cast<size_t>(m) * p.D + tid * CH);
 #pragma unroll
-        for (int q = 0; q < kChunk / 4; ++q) o[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        for (int q = 0; q < CH / 4; ++q) o[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
       }
       continue;
     }
@@ -237,7 +249,7 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
       chunk_butterflies(v);
       lane_butterflies<BLOCK>(v, lane);
 #pragma unroll
-      for (int i = 0; i < kChunk; i += 2) {
+      for (int i = 0; i < CH; i += 2) {
         const float2 r = __fmul2_rn(make_float2(v[i], v[i + 1]), norm2);
         v[i] = r.x; v[i + 1] = r.y;
       }
@@ -248,9 +260,9 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
         refill();
       }
       if (active) {
-        __half *dst = static_cast<__half *>(p.out) + static_cast<size_t>(m) * p.D + tid * kChunk;
+        __half *dst = static_cast<__half *>(p.out) + static_cast<size_t>(m) * p.D + tid * CH;
 #pragma unroll
-        for (int q = 0; q < kChunk / 8; ++q) {
+        for (int q = 0; q < CH / 8; ++q) {
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -265,7 +277,7 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
     if constexpr (OUT == kOutQ8) {
       float amax = 0.0f;
 #pragma unroll
-      for (int i = 0; i < kChunk; i += 2) amax = fmaxf(amax, fmaxf(fabsf(v[i]), fabsf(v[i + 1])));
+      for (int i = 0; i < CH; i += 2) amax = fmaxf(amax, fmaxf(fabsf(v[i]), fabsf(v[i + 1])));
       float row_max = cta_reduce(amax, true);
       refill();
       if (p.scale_mode == 1) {  // a shard of a longer row: hand the local maximum to the caller
@@ -277,16 +289,16 @@ __global__ void __launch_bounds__(256) rot_q8_tma_kernel(const __grid_constant__
       const float rs = __fdiv_rn(1.0f, scale);
       const float2 rs2 = make_float2(rs, rs);
       if (active) {
-        uint32_t w[kChunk / 4];
+        uint32_t w[CH / 4];
 #pragma unroll
-        for (int j = 0; j < kChunk / 4; ++j) {
+        for (int j = 0; j < CH / 4; ++j) {
           const float2 y0 = __fmul2_rn(make_float2(v[4 * j], v[4 * j + 1]), rs2);
           const float2 y1 = __fmul2_rn(make_float2(v[4 * j + 2], v[4 * j + 3]), rs2);
           w[j] = pack4_s8(__float2int_rn(y0.x), __float2int_rn(y0.y), __float2int_rn(y1.x), __float2int_rn(y1.y));
         }
-        uint4 *d4 = reinterpret_cast<uint4 *>(static_cast<int8_t *>(p.out) + static_cast<size_t>(m) * p.D + tid * kChunk);
+        uint4 *d4 = reinterpret_cast<uint4 *>(static_cast<int8_t *>(p.out) + static_cast<size_t>(m) * p.D + tid * CH);
 #pragma unroll
-        for (int j = 0; j < kChunk / 16; ++j) d4[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        for (int j = 0; j < CH / 16; ++j) d4[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
       }
       if (tid == 0) p.sa[m] = scale;
     }
@@ -318,23 +330,32 @@ int resident_ctas(const void *fn, int threads, size_t smem) {
   return n;
 }
 
-template <int IN, int BLOCK, int FRONT, bool LN, int OUT>
+template <int IN, int BLOCK, int FRONT, bool LN, int OUT, int CH = kChunk>
 cudaError_t launch_final(const RotTmaArgs &a, int threads, size_t smem, int sms, cudaStream_t stream) {
-  auto *fn = rot_q8_tma_kernel<IN, BLOCK, FRONT, LN, OUT>;
+  auto *fn = rot_q8_tma_kernel<IN, BLOCK, FRONT, LN, OUT, CH>;
   const long long resident = static_cast<long long>(sms) * resident_ctas(reinterpret_cast<const void *>(fn), threads, smem);
   const int grid = static_cast<int>(a.M < resident ? a.M : resident);
-  fn<<<grid, threads, smem, stream>>>(a);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.overlap ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, fn, a);
 }
 
-template <int IN, int BLOCK>
+template <int IN, int BLOCK, int CH>
 cudaError_t launch_rot(const RotTmaArgs &a, int threads, size_t smem, int sms, int mode, int out_hr, cudaStream_t stream) {
   if (out_hr) {
-    return mode == 1 ? launch_final<IN, BLOCK, kSwiglu, false, kOutHr>(a, threads, smem, sms, stream)
-                     : launch_final<IN, BLOCK, kPlain, false, kOutHr>(a, threads, smem, sms, stream);
+    return mode == 1 ? launch_final<IN, BLOCK, kSwiglu, false, kOutHr, CH>(a, threads, smem, sms, stream)
+                     : launch_final<IN, BLOCK, kPlain, false, kOutHr, CH>(a, threads, smem, sms, stream);
   }
-  return mode == 1 ? launch_final<IN, BLOCK, kSwiglu, false, kOutQ8>(a, threads, smem, sms, stream)
-                   : launch_final<IN, BLOCK, kPlain, false, kOutQ8>(a, threads, smem, sms, stream);
+  return mode == 1 ? launch_final<IN, BLOCK, kSwiglu, false, kOutQ8, CH>(a, threads, smem, sms, stream)
+                   : launch_final<IN, BLOCK, kPlain, false, kOutQ8, CH>(a, threads, smem, sms, stream);
 }
 
 template <int BLOCK, bool LN>
@@ -347,7 +368,7 @@ cudaError_t launch_norm(const RotTmaArgs &a, int threads, size_t smem, int sms, 
   }
 }
 
-void plan(int D, int esize, bool gates, int stages_wanted, RotTmaArgs *a, int *threads, size_t *smem) {
+void plan(int D, int esize, bool gates, int stages_wanted, int chunk, RotTmaArgs *a, int *threads, size_t *smem) {
   const int row = (D * esize + 1023) / 1024 * 1024;
   a->gate_offset = row;
   a->stage_bytes = esize == 4 ? 3 * row : gates ? 2 * row : row;  // fp32 rows carry their scale' and shift vectors
@@ -357,8 +378,8 @@ void plan(int D, int esize, bool gates, int stages_wanted, RotTmaArgs *a, int *t
   if (s > kMaxStages) s = kMaxStages;
   while (s > 1 && static_cast<size_t>(s) * a->stage_bytes + 2048 > 232448) --s;
   a->stages = s;
-  *threads = (D / kChunk + 31) / 32 * 32;
-  *smem = 1024 + static_cast<size_t>(s) * a->stage_bytes + 256;
+  *threads = (D / chunk + 31) / 32 * 32;
+  *smem = 1024 + static_cast<size_t>(s) * a->stage_bytes + 512;
 }
 
 }  // namespace
@@ -369,23 +390,30 @@ bool rot_q8_tma_supported(int x_dtype, int D) {
 bool norm_mod_q8_tma_supported(int D) { return D % kChunk == 0 && D / 32 <= 256; }  // the box holds D / 32 lines
 
 cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, float *sa, int M, int D, int block,
-                              int mode, int out_hr, int scale_mode, int stages_wanted, int sms, int *status,
-                              cudaStream_t stream) {
+                              int mode, int out_hr, int scale_mode, int stages_wanted, int chunk_wanted, int sms,
+                              int *status, cudaStream_t stream, bool overlap) {
   RotTmaArgs a = {};
   a.map = map; a.out = out; a.sa = sa; a.status = status; a.M = M; a.D = D; a.scale_mode = scale_mode;
+  a.overlap = overlap ? 1 : 0;
   a.normaliser = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
   int threads;
   size_t smem;
-  plan(D, 2, mode == 1, stages_wanted, &a, &threads, &smem);
-  if (threads > 256 || smem > 232448) return cudaErrorInvalidConfiguration;
-#define H3B_ROT(IN)                                                                    \
-  switch (block) {                                                                     \
-    case 64: return launch_rot<IN, 64>(a, threads, smem, sms, mode, out_hr, stream);   \
-    case 128: return launch_rot<IN, 128>(a, threads, smem, sms, mode, out_hr, stream); \
-    default: return launch_rot<IN, 256>(a, threads, smem, sms, mode, out_hr, stream);  \
+  // measured: half-line chunks (twice the threads) win for short rows, whole lines from about 3840 channels on
+  const int chunk = chunk_wanted == 32 || chunk_wanted == 64 ? chunk_wanted : (D <= 3072 ? 32 : kChunk);
+  plan(D, 2, mode == 1, stages_wanted, chunk, &a, &threads, &smem);
+  if (threads > (chunk == 32 ? 512 : 256) || smem > 232448) return cudaErrorInvalidConfiguration;
+#define H3B_ROT(IN, CH)                                                                    \
+  switch (block) {                                                                         \
+    case 64: return launch_rot<IN, 64, CH>(a, threads, smem, sms, mode, out_hr, stream);   \
+    case 128: return launch_rot<IN, 128, CH>(a, threads, smem, sms, mode, out_hr, stream); \
+    default: return launch_rot<IN, 256, CH>(a, threads, smem, sms, mode, out_hr, stream);  \
   }
-  if (x_dtype == kDtypeF16) { H3B_ROT(1) }
-  H3B_ROT(0)
+  if (chunk == 32) {
+    if (x_dtype == kDtypeF16) { H3B_ROT(1, 32) }
+    H3B_ROT(0, 32)
+  }
+  if (x_dtype == kDtypeF16) { H3B_ROT(1, 64) }
+  H3B_ROT(0, 64)
 #undef H3B_ROT
 }
 
@@ -399,7 +427,7 @@ cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const CUtensorMap &ma
   a.normaliser = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
   int threads;
   size_t smem;
-  plan(D, 4, false, stages_wanted, &a, &threads, &smem);
+  plan(D, 4, false, stages_wanted, kChunk, &a, &threads, &smem);
   if (threads > 256 || smem > 232448) return cudaErrorInvalidConfiguration;
   switch (block) {
     case 64: return ln ? launch_norm<64, true>(a, threads, smem, sms, out_kind, stream) : launch_norm<64, false>(a, threads, smem, sms, out_kind, stream);

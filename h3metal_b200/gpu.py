@@ -60,6 +60,7 @@ def _signatures():
         "h3b_sm_count": (i32, [vp]),
         "h3b_set_stream": (i32, [vp, vp]),
         "h3b_use_own_stream": (i32, [vp]),
+        "h3b_set_launch_overlap": (i32, [vp, i32]),
         "h3b_rot_q8": (i32, [vp, vp, i32, i64, vp, vp, i32, i32, i32, i32, i32]),
         "h3b_norm_mod_q8": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, ctypes.c_float, i32, i32, vp, vp]),
         "h3b_rot_amax": (i32, [vp, vp, i32, i64, vp, i32, i32, i32, i32]),
@@ -82,7 +83,7 @@ def _signatures():
                                      i32]),
         "h3b_gemm_tile_n": (i32, [vp, i32, i32]),
         "h3b_gemm_set_policy": (i32, [vp, i32, i32, i32]),
-        "h3b_rot_set_policy": (i32, [vp, i32, i32]),
+        "h3b_rot_set_policy": (i32, [vp, i32, i32, i32]),
         "h3b_selftest_expire_wait": (i32, [vp]),
         "h3b_commit": (None, [vp]),
         "h3b_wait": (dbl, [vp]),
@@ -237,6 +238,11 @@ class Gpu:
         self.stream = stream if stream is not None else torch.cuda.current_stream(self.torch_device)
         if lib().h3b_set_stream(self.ctx, ctypes.c_void_p(self.stream.cuda_stream)):
             raise GpuError(_err())
+
+    def set_launch_overlap(self, on: bool):
+        """Programmatic dependent launch of the path's kernels (off by default): a kernel's set-up overlaps the tail
+        of the kernel before it; every kernel still waits for its predecessor before touching global memory."""
+        self._check(lib().h3b_set_launch_overlap(self.ctx, 1 if on else 0))
 
     def kernel(self, file: str, fn: str, **macros) -> Kernel:
         key = (file, fn, tuple(sorted(macros.items())))
@@ -415,12 +421,13 @@ class Gpu:
     def gemm_tile_n(self, N: int, lora: bool) -> int:
         return lib().h3b_gemm_tile_n(self.ctx, N, int(lora))
 
-    def set_policy(self, tile_n: int = 0, band: int = 0, rot_threads: int = 0, rot_stages: int = 0, pair: int = 0):
+    def set_policy(self, tile_n: int = 0, band: int = 0, rot_threads: int = 0, rot_stages: int = 0, pair: int = 0,
+                   rot_chunk: int = 0):
         """Overrides of the library's own choices (0 = automatic), for tuning sweeps and for tests that want a
         particular kernel variant. rot_stages = -1 selects the register-fed rotate+quantise kernel; pair = -1 / 1 keeps
-        the product off / on CTA pairs."""
+        the product off / on CTA pairs; rot_chunk = 32 / 64 sets the channels per thread of the TMA-fed kernel."""
         self._check(lib().h3b_gemm_set_policy(self.ctx, tile_n, band, pair))
-        self._check(lib().h3b_rot_set_policy(self.ctx, rot_threads, rot_stages))
+        self._check(lib().h3b_rot_set_policy(self.ctx, rot_threads, rot_stages, rot_chunk))
 
     # -- execution ------------------------------------------------------------------------------------------------
     def launch(self, k: Kernel, grid, threads, args, params: bytes = b"", params_index: int | None = None,

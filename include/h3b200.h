@@ -61,6 +61,14 @@ H3B_API int h3b_sm_count(h3b_ctx *ctx);
 H3B_API int h3b_set_stream(h3b_ctx *ctx, void *cuda_stream);
 H3B_API int h3b_use_own_stream(h3b_ctx *ctx);
 
+/* Launch overlap (off by default): with on != 0 the product and the TMA-fed rotate+quantise kernels are launched with
+ * CUDA's programmatic stream serialization, so a kernel's set-up (barriers, tensor memory, descriptor prefetch) runs
+ * while the kernel before it in the stream drains; each kernel waits for its predecessor's completion before it
+ * touches global memory, so results and ordering are unchanged. Measured on B200: 3 % faster on a chain of two 25 us
+ * kernels (one 3072 x 3072 linear over 4096 tokens), 3 % slower on a block of 60-270 us products, hence the default.
+ * No reference counterpart (Metal encodes one command buffer, src/capi.mm:51-64). Returns 0. */
+H3B_API int h3b_set_launch_overlap(h3b_ctx *ctx, int on);
+
 /* Rotate + per-token int8 quantise. Replaces the dispatch of the Metal kernel rot_q8
  * (kernels/ops.metal:274-334; parameter block RotQParams kernels/params.h:25-29; launcher h3metal/ops.py:214-222).
  *   x        [M][x_stride] of x_dtype (H3B_BF16 / H3B_F16 / H3B_F32); with mode 1 columns D..2D-1 hold the gates
@@ -221,9 +229,10 @@ H3B_API int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int lora);
 H3B_API int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band, int pair);
 /* Tuning of the rotate+quantise kernel. tma_stages: rows a CTA keeps in flight in shared memory (1..4), 0 =
  * automatic, -1 = do not use the TMA-fed kernel. threads_target: CTA size target of the register-fed kernel that
- * serves fp32 inputs, rows over 16384 channels and tma_stages = -1 (0 = automatic). The counterpart of the NSG/MAXB
- * geometry of h3metal/ops.py:193-197. Returns 0. */
-H3B_API int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target, int tma_stages);
+ * serves fp32 inputs, rows over 16384 channels and tma_stages = -1 (0 = automatic). chunk: channels a thread of the
+ * TMA-fed kernel owns, 32 or 64 (0 = automatic). The counterpart of the NSG/MAXB geometry of
+ * h3metal/ops.py:193-197. Returns 0. */
+H3B_API int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target, int tma_stages, int chunk);
 
 /* Self-test of the error path the kernels share. Every device-side wait in this library is bounded: when one runs
  * out the kernel records a code in the context's status word, winds down and returns, and the next h3b_wait reports

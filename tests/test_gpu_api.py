@@ -98,3 +98,35 @@ def test_an_expired_device_wait_surfaces_at_wait_and_the_context_survives(gpu):
              sa=gpu.upload(np.ones(128, np.float32)), tile=(128, 64, 4))
     gpu.wait()
     assert np.array_equal(out.numpy(), gemm_ref.int32_product(a, w))
+
+
+def test_launch_overlap_changes_no_result(gpu):
+    """With programmatic dependent launch every kernel still waits for its predecessor before it touches global
+    memory: a chain rotate+quantise -> product -> swiglu rotate+quantise -> product gives the same bits either way."""
+    import numpy as np
+    import oracle
+    from h3metal_b200 import ops
+    rng = np.random.default_rng(21)
+    M, D, F = 640, 1024, 1536
+    x = gpu.upload(oracle.bf16_round_bits((rng.standard_normal((M, D)) * 2).astype(np.float32)), "bf16")
+    w1 = ops.QWeight("q8", gpu.upload(rng.integers(-127, 128, size=(2 * F, D), dtype=np.int8)),
+                     gpu.upload(rng.uniform(1e-3, 2e-3, size=2 * F).astype(np.float32)), 2 * F, D)
+    w2 = ops.QWeight("q8", gpu.upload(rng.integers(-127, 128, size=(D, F), dtype=np.int8)),
+                     gpu.upload(rng.uniform(1e-3, 2e-3, size=D).astype(np.float32)), D, F)
+    results = []
+    for on in (False, True, True):
+        gpu.set_launch_overlap(on)
+        try:
+            a1, s1, h = gpu.empty((M, D), "i8"), gpu.empty((M,), "f32"), gpu.empty((M, 2 * F), "bf16")
+            a2, s2, y = gpu.empty((M, F), "i8"), gpu.empty((M,), "f32"), gpu.empty((M, D), "bf16")
+            for _ in range(3):  # back to back, so that kernels do follow kernels in the stream
+                ops.rot_q8(gpu, x, a1, s1, M, D, block=128)
+                ops.gemm(gpu, a1, w1, h, M, sa=s1)
+                ops.rot_q8(gpu, h, a2, s2, M, F, swiglu=True, block=128)
+                ops.gemm(gpu, a2, w2, y, M, sa=s2)
+            gpu.wait()
+            results.append((a2.numpy().copy(), y.numpy().copy()))
+        finally:
+            gpu.set_launch_overlap(False)
+    for codes, out in results[1:]:
+        assert np.array_equal(codes, results[0][0]) and np.array_equal(out, results[0][1])

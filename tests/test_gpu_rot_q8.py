@@ -29,11 +29,13 @@ def _bits(rng, M, cols, scale=2.0, outliers=0, D=None):
 
 def _run(gpu, xh, dtype, M, D, block, swiglu, x_stride=None, out_hr=False, variant="tma"):
     """variant: "tma" = the library's choice (rows staged in shared memory by TMA for 16-bit inputs of up to 16384
-    channels), "tma2" / "tma4" = the same with a ring of 2 / 4 rows, "regs" = the register-fed kernel."""
+    channels), "tma2" / "tma4" = the same with a ring of 2 / 4 rows, "tma_c32" / "tma_c64" = the same with 32 / 64
+    channels per thread, "regs" = the register-fed kernel."""
     X = gpu.upload(xh, dtype)
     out = gpu.empty((M, D), "f16" if out_hr else "i8")
     sa = gpu.empty((M,), "f32")
-    gpu.set_policy(rot_stages={"tma": 0, "tma2": 2, "tma4": 4, "regs": -1}[variant])
+    gpu.set_policy(rot_stages={"tma2": 2, "tma4": 4, "regs": -1}.get(variant, 0),
+                   rot_chunk={"tma_c32": 32, "tma_c64": 64}.get(variant, 0))
     try:
         ops.rot_q8(gpu, X, out, None if out_hr else sa, M, D, swiglu=swiglu, block=block, x_stride=x_stride,
                    out_hr=out_hr)
@@ -53,7 +55,7 @@ def _check_codes(gq, gs, q, s, exact):
         assert ulp_distance(gs, s).max() <= 4
 
 
-@pytest.mark.parametrize("variant", ["tma", "regs"])
+@pytest.mark.parametrize("variant", ["tma", "tma_c32", "tma_c64", "regs"])
 @pytest.mark.parametrize("block", [64, 128, 256])
 @pytest.mark.parametrize("M,D", [(1, 256), (19, 512), (7, 3072), (33, 3840), (5, 6144), (9, 16384), (3, 32768),
                                  (127, 768), (129, 1280), (1500, 2048)])
@@ -80,7 +82,7 @@ def test_other_input_types_bit_exact(gpu, dtype, block):
     _check_codes(gq, gs, q, s, exact=True)
 
 
-@pytest.mark.parametrize("variant", ["tma", "tma2", "tma4", "regs"])
+@pytest.mark.parametrize("variant", ["tma", "tma2", "tma4", "tma_c32", "tma_c64", "regs"])
 @pytest.mark.parametrize("block,M,D", [(256, 19, 14336), (128, 33, 10240), (128, 17, 16384), (64, 8, 1024),
                                        (128, 700, 1280)])
 def test_swiglu_within_budget(gpu, variant, block, M, D):
@@ -109,7 +111,7 @@ def test_reference_golden_rotation_bound(gpu, golden):
         assert np.abs(half.astype(np.float64) - want).max() / np.abs(want).max() < 2e-3
 
 
-@pytest.mark.parametrize("variant", ["tma", "regs"])
+@pytest.mark.parametrize("variant", ["tma", "tma_c32", "regs"])
 @pytest.mark.parametrize("block", [128, 256])
 def test_rotated_half_output(gpu, variant, block):
     rng = np.random.default_rng(11)
