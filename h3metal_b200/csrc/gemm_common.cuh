@@ -24,10 +24,12 @@ constexpr int kThreads = 192;
 constexpr int kBarrierBytes = 256;
 // Row-parallel push: the transposition buffers of the four epilogue warps. int32 partials need 8 KB per warp and use
 // the (then idle) column staging as well; bf16 partials need 4 KB per warp behind the column staging.
-__host__ __device__ constexpr int push_bytes(int bn) { return 32768 - 16 * bn * 4 > 16384 ? 32768 - 16 * bn * 4 : 16384; }
+constexpr int kColStageWarps = 4;  // epilogue warps, each with its own copy of the tile's column scales and biases
+__host__ __device__ constexpr int push_bytes(int bn) {
+  return 32768 - kColStageWarps * 2 * bn * 4 > 16384 ? 32768 - kColStageWarps * 2 * bn * 4 : 16384;
+}
 
 __host__ __device__ constexpr int stage_bytes(int bn) { return kABytes + bn * kBKBytes; }
-__host__ __device__ constexpr int lora_bytes(int bn, int R) { return (R / kLoraChunk) * (kLoraTBytes + bn * kLoraChunk * 2); }
 
 struct TileCoord {
   int m_blk, n_blk;

@@ -13,8 +13,9 @@
 //           guarded by a full/empty mbarrier pair. Rows or K beyond the tensor are zero-filled by TMA.
 //   warp 1  MMA issuer: one thread issues tcgen05.mma kind::i8 (M 128, N BN, K 32 per instruction, four per
 //           stage) accumulating int32 in tensor memory; tcgen05.commit releases the stage to the producer and,
-//           after the last K block, hands the accumulator to the epilogue. With a LoRA term the same thread first
-//           issues kind::f16 MMAs (fp16 x fp16 -> fp32) of the tile's T and B' slices into a second TMEM region.
+//           after the last K block, hands the accumulator to the epilogue. With a LoRA term the tile's T and B'
+//           slices come through the same ring ahead of the K blocks (one stage holds 64 ranks) and the same thread
+//           issues kind::f16 MMAs (fp16 x fp16 -> fp32) on them into a second TMEM region.
 //   warps 2-5  epilogue: each warp owns 32 accumulator rows (its TMEM lane quarter), reads 32 columns at a time
 //           with tcgen05.ld, applies scales, bias and the low-rank term and stores 64-byte row segments.
 // Accumulators are double-buffered in TMEM (2 x BN columns of the 512) so the epilogue of one tile overlaps the
@@ -36,7 +37,7 @@ using namespace gemm;
 template <int BN, int ACC_STAGES, bool LORA, int EPI_WARPS, bool PUSH = false>
 __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const __grid_constant__ GemmLaunch g,
                                                                            const int stages) {
-  static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "one or two epilogue warps per TMEM lane quarter");
+  static_assert(EPI_WARPS == 4, "one epilogue warp per TMEM lane quarter");
   static_assert(!(PUSH && (LORA || EPI_WARPS != 4)), "the row-parallel push has no low-rank term");
   static_assert(ACC_STAGES * BN <= (LORA ? kLowBase : kTmemCols), "accumulators do not fit tensor memory");
   extern __shared__ uint8_t smem_raw[];
@@ -47,23 +48,23 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
   constexpr uint32_t kWBytes = BN * kBKBytes;
   constexpr uint32_t kStage = kABytes + kWBytes;
   constexpr uint32_t kLoraBBytes = BN * kLoraChunk * 2;
+  // The low-rank term's operands travel through the same ring as the main operands: before a tile's K blocks come
+  // `lora_blocks` stages that hold up to two 32-rank chunks each, T in the A part and B' in the W part of the stage.
   const int chunks = LORA ? g.R / kLoraChunk : 0;
-  const uint32_t lora_t = base + stages * kStage;
-  const uint32_t lora_b = lora_t + chunks * kLoraTBytes;
-  const uint32_t bars_off = stages * kStage + chunks * (kLoraTBytes + kLoraBBytes);
+  const int lora_blocks = (chunks + 1) / 2;
+  const uint32_t bars_off = stages * kStage;
   const uint32_t bars = base + bars_off;
   auto full_bar = [&](int i) { return bars + 8u * i; };
   auto empty_bar = [&](int i) { return bars + 64u + 8u * i; };
   auto acc_full_bar = [&](int i) { return bars + 128u + 8u * i; };
   auto acc_empty_bar = [&](int i) { return bars + 144u + 8u * i; };
-  const uint32_t lora_full_bar = bars + 160u, lora_empty_bar = bars + 168u;
   volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(base_ptr + bars_off + 176);
   volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + bars_off + 180);
   float *col_stage = reinterpret_cast<float *>(base_ptr + bars_off + kBarrierBytes);  // [EPI_WARPS][2][BN]: sw, bias
   // PUSH: transposition buffers of outgoing chunk pairs. int32 partials: 8 KB per epilogue warp from the start of the
   // column staging (which raw accumulators do not use); bf16 partials: 4 KB per warp behind the column staging.
   uint4 *xpose_raw = reinterpret_cast<uint4 *>(col_stage);
-  uint4 *xpose_bf16 = reinterpret_cast<uint4 *>(base_ptr + bars_off + kBarrierBytes + 16 * BN * sizeof(float));
+  uint4 *xpose_bf16 = reinterpret_cast<uint4 *>(base_ptr + bars_off + kBarrierBytes + kColStageWarps * 2 * BN * sizeof(float));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (g.M + kBM - 1) / kBM, n_tiles = (g.N + BN - 1) / BN;
@@ -85,8 +86,6 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
       mbar_init(acc_full_bar(i), 1);
       mbar_init(acc_empty_bar(i), EPI_WARPS);  // one arrival per epilogue warp
     }
-    mbar_init(lora_full_bar, 1);
-    mbar_init(lora_empty_bar, 1);
     *cta_abort = 0;
     fence_barrier_init();
   }
@@ -106,20 +105,26 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
   if (warp == 0) {
     // ---------------------------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      uint32_t it = 0, lt = 0;
+      uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, g.band);
         const int m0 = tc.m_blk * kBM, n0 = tc.n_blk * BN;
         if (LORA) {
-          ok = mbar_wait(lora_empty_bar, (lt & 1u) ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
-          if (!ok) break;
-          mbar_arrive_expect_tx(lora_full_bar, chunks * (kLoraTBytes + kLoraBBytes));
-          for (int c = 0; c < chunks; ++c) {
-            tma_load_2d(lora_t + c * kLoraTBytes, &g.map_t, lora_full_bar, c * kLoraChunk, m0);
-            tma_load_2d(lora_b + c * kLoraBBytes, &g.map_b, lora_full_bar, c * kLoraChunk, n0);
+          for (int j = 0; ok && j < lora_blocks; ++j, ++it) {
+            const int s = it % stages;
+            const uint32_t ph = (it / stages) & 1u;
+            ok = mbar_wait(empty_bar(s), ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
+            if (!ok) break;
+            const int n_here = min(2, chunks - 2 * j);
+            mbar_arrive_expect_tx(full_bar(s), n_here * (kLoraTBytes + kLoraBBytes));
+            const uint32_t dst = base + s * kStage;
+            for (int c = 0; c < n_here; ++c) {
+              tma_load_2d(dst + c * kLoraTBytes, &g.map_t, full_bar(s), (2 * j + c) * kLoraChunk, m0);
+              tma_load_2d(dst + kABytes + c * kLoraBBytes, &g.map_b, full_bar(s), (2 * j + c) * kLoraChunk, n0);
+            }
           }
-          ++lt;
+          if (!ok) break;
         }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % stages;
@@ -140,10 +145,6 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
           mbar_wait(full_bar(j % stages), (j / stages) & 1u, &dummy_abort, g.status, kStatusDrainTimeout,
                     kDrainLimitCycles);
         }
-        if (LORA && lt > 0) {
-          int dummy_abort = 0;
-          mbar_wait(lora_full_bar, (lt - 1) & 1u, &dummy_abort, g.status, kStatusDrainTimeout, kDrainLimitCycles);
-        }
       }
     }
   } else if (warp == 1) {
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
     if (lane == 0) {
       constexpr uint32_t idesc_i8 = umma_instr_desc(2, 1, kBM, BN);   // s32 accumulate, s8 x s8
       constexpr uint32_t idesc_f16 = umma_instr_desc(1, 0, kBM, BN);  // f32 accumulate, f16 x f16
-      uint32_t it = 0, at = 0, lt = 0;
+      uint32_t it = 0, at = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++at) {
         const int as = at % ACC_STAGES;
@@ -167,19 +168,25 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
             k0 = g.ranges[2 * tc.n_blk];
             k1 = g.ranges[2 * tc.n_blk + 1];
           }
-          ok = mbar_wait(lora_full_bar, lt & 1u, cta_abort, g.status, kStatusMmaTimeout);
-          if (!ok) break;
-          tc_fence_after_sync();
           const uint32_t d_low = tmem_base + kLowBase + as * BN;
-          for (int kk = k0; kk < k1; kk += 16) {  // one kind::f16 instruction covers 16 ranks = 32 bytes
-            const int c = kk / kLoraChunk;
-            const uint32_t koff = ((kk % kLoraChunk) * 2) >> 4;
-            const uint64_t td = umma_smem_desc(lora_t + c * kLoraTBytes, 512, 4) + koff;
-            const uint64_t bd = umma_smem_desc(lora_b + c * kLoraBBytes, 512, 4) + koff;
-            umma_f16(d_low, td, bd, idesc_f16, kk != k0 ? 1u : 0u);
+          for (int j = 0; ok && j < lora_blocks; ++j, ++it) {
+            const int s = it % stages;
+            const uint32_t ph = (it / stages) & 1u;
+            ok = mbar_wait(full_bar(s), ph, cta_abort, g.status, kStatusMmaTimeout);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t a_addr = base + s * kStage;
+            const int lo = max(k0, 2 * j * kLoraChunk), hi = min(k1, (2 * j + 2) * kLoraChunk);
+            for (int kk = lo; kk < hi; kk += 16) {  // one kind::f16 instruction covers 16 ranks = 32 bytes
+              const int c = kk / kLoraChunk - 2 * j;
+              const uint32_t koff = ((kk % kLoraChunk) * 2) >> 4;
+              const uint64_t td = umma_smem_desc(a_addr + c * kLoraTBytes, 512, 4) + koff;
+              const uint64_t bd = umma_smem_desc(a_addr + kABytes + c * kLoraBBytes, 512, 4) + koff;
+              umma_f16(d_low, td, bd, idesc_f16, kk != k0 ? 1u : 0u);
+            }
+            umma_commit(empty_bar(s));  // the stage may be refilled once these MMAs have read it
           }
-          umma_commit(lora_empty_bar);  // the LoRA tiles may be overwritten once these MMAs have read them
-          ++lt;
+          if (!ok) break;
         }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % stages;
@@ -202,14 +209,9 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
     }
   } else {
     // ---------------------------------------------------------------------------------- epilogue (warps 2 ..)
-    // A warp may only read the TMEM lanes of its quarter (warp index mod 4). With eight epilogue warps two warps
-    // share a quarter and split the tile's columns between them.
+    // A warp may only read the TMEM lanes of its quarter (warp index mod 4).
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;                          // 0, or 1 for the second warp of a quarter
-    constexpr int kChunks = BN / 32;
-    constexpr int kPerWarp = EPI_WARPS == 8 && kChunks >= 2 ? kChunks / 2 : kChunks;
-    const int c_begin = EPI_WARPS == 8 && kChunks >= 2 ? half * kPerWarp : 0;
-    const int c_end = (EPI_WARPS == 8 && kChunks < 2 && half == 1) ? c_begin : c_begin + kPerWarp;
+    constexpr int c_begin = 0, c_end = BN / 32;
     const int row = quarter * 32 + lane;
     const bool raw = g.c_dtype == kDtypeI32;
     const size_t esize = (g.c_dtype == kDtypeF32 || raw) ? 4 : 2;
@@ -252,12 +254,12 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN;
       const uint32_t t_low = t_acc + kLowBase;
-      // two register sets: the TMEM loads of the next 32 columns are in flight while this chunk is finished
-      uint32_t acc_a[32], low_a[32], acc_b[32], low_b[32];
       auto fetch = [&](int c, uint32_t (&acc)[32], uint32_t (&low)[32]) {
         tmem_ld_32x32b_x32(t_acc + c * 32, acc);
         if (LORA && has_low) tmem_ld_32x32b_x32(t_low + c * 32, low);
       };
+      // two register sets: the TMEM loads of the next 32 columns are in flight while this chunk is finished
+      uint32_t acc_a[32], low_a[32], acc_b[32], low_b[32];
       if (c_begin < c_end) fetch(c_begin, acc_a, low_a);
 #pragma unroll 1
       for (int c = c_begin; c < c_end; c += 2) {
@@ -317,8 +319,8 @@ cudaError_t configure_one() {
 size_t gemm_smem_bytes(int bn, int R, int stages) {
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return 0;
   if (R % kLoraChunk) return 0;
-  return 1024 + static_cast<size_t>(stages) * stage_bytes(bn) + lora_bytes(bn, R) + kBarrierBytes +
-         16 * static_cast<size_t>(bn) * sizeof(float);  // column staging for up to eight epilogue warps
+  return 1024 + static_cast<size_t>(stages) * stage_bytes(bn) + kBarrierBytes +
+         static_cast<size_t>(kColStageWarps) * 2 * bn * sizeof(float);  // column scales and biases, per epilogue warp
 }
 
 int gemm_pick_stages(int bn, int R, size_t smem_optin, bool push) {
@@ -361,8 +363,9 @@ cudaError_t launch_gemm_w8a8(const GemmLaunch &g, int stages, cudaStream_t strea
     case 128: return lora ? launch_one<128, 2, true, 4>(g, stages, stream) : launch_one<128, 2, false, 4>(g, stages, stream);
     case 256:
       // A low-rank term on 256-column tiles leaves room for ONE accumulator pair in tensor memory, so its epilogue
-      // (about 3 us per tile) does not overlap the next tile's main loop. Measured alternatives were slower: a
-      // second epilogue warp per lane quarter (-15 %) and 128-column tiles with two accumulator pairs (-25 %).
+      // does not overlap the next tile's main loop. Measured alternatives: a second epilogue warp per lane quarter
+      // changes nothing (the exposed time is the hand-over and the stores, not instruction issue); 128-column tiles
+      // with two accumulator pairs are 25 % slower (operand reads from shared memory per MMA double).
       return lora ? launch_one<256, 1, true, 4>(g, stages, stream) : launch_one<256, 2, false, 4>(g, stages, stream);
     default: return cudaErrorInvalidValue;
   }
