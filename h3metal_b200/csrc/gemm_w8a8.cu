@@ -365,7 +365,9 @@ cudaError_t launch_gemm_w8a8(const GemmLaunch &g, int stages, cudaStream_t strea
       // A low-rank term on 256-column tiles leaves room for ONE accumulator pair in tensor memory, so its epilogue
       // does not overlap the next tile's main loop. Measured alternatives: a second epilogue warp per lane quarter
       // changes nothing (the exposed time is the hand-over and the stores, not instruction issue); 128-column tiles
-      // with two accumulator pairs are 25 % slower (operand reads from shared memory per MMA double).
+      // with two accumulator pairs are 25 % slower, and 160-column tiles with two main accumulators and one shared
+      // low-rank accumulator (480 columns) 15-20 % slower: the narrower the MMA, the more operand bytes it reads from
+      // shared memory per multiply (96 bytes per clock at 256 columns, 115 at 160, 128 - the limit - at 128).
       return lora ? launch_one<256, 1, true, 4>(g, stages, stream) : launch_one<256, 2, false, 4>(g, stages, stream);
     default: return cudaErrorInvalidValue;
   }
