@@ -624,9 +624,10 @@ int h3b_gemm_w8a8_push(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const in
                       nullptr, 0, 0, nullptr, true, nullptr, nullptr, 0, slots, world, rows_per_gpu);
 }
 
-int h3b_reduce_dequant(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride, int stage_dtype,
-                       int world, const float *sa, const float *sw, const float *bias, void *const *outs, int n_out,
-                       int c_dtype, int64_t c_stride, int rows, int N, int row0) {
+static int reduce_enqueue(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride, int stage_dtype,
+                          int world, const float *sa, const float *sw, const float *bias, void *const *outs, int n_out,
+                          int c_dtype, int64_t c_stride, int rows, int N, int row0, const uint8_t *rtype,
+                          const float *gate, int64_t g_stride) {
   if (!ctx) return fail("null context");
   if (!stage || !outs) return fail("reduce_dequant: null tensor argument");
   if (world < 1 || world > h3b::kMaxPeers || n_out < 1 || n_out > h3b::kMaxPeers) return fail("reduce_dequant: 1 to 8 slots and outputs");
@@ -642,6 +643,11 @@ int h3b_reduce_dequant(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int
   r.stage = stage; r.slot_stride = slot_stride; r.stage_stride = stage_stride; r.stage_dtype = stage_dtype; r.world = world;
   r.sa = sa; r.sw = sw; r.bias = bias; r.n_out = n_out; r.c_stride = c_stride; r.c_dtype = c_dtype; r.rows = rows; r.N = N;
   r.row0 = row0;
+  if (gate) {
+    if (!rtype) return fail("reduce_dequant (gated): null row types");
+    if (g_stride < N || (g_stride * 4) % 16 || reinterpret_cast<uintptr_t>(gate) % 16) return fail("reduce_dequant (gated): gate rows must be 16-byte aligned and at least N long");
+    r.rtype = rtype; r.gate = gate; r.g_stride = g_stride;
+  }
   for (int i = 0; i < n_out; ++i) {
     if (!outs[i] || reinterpret_cast<uintptr_t>(outs[i]) % 16) return fail("reduce_dequant: null or misaligned output");
     r.out[i] = outs[i];
@@ -649,6 +655,22 @@ int h3b_reduce_dequant(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int
   cudaEvent_t ps = nullptr;
   if (ctx->before_launch(&ps)) return -1;
   return ctx->after_launch("reduce_dequant launch", h3b::launch_reduce_dequant(r, ctx->prop.multiProcessorCount, ctx->stream));
+}
+
+int h3b_reduce_dequant(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride, int stage_dtype,
+                       int world, const float *sa, const float *sw, const float *bias, void *const *outs, int n_out,
+                       int c_dtype, int64_t c_stride, int rows, int N, int row0) {
+  return reduce_enqueue(ctx, stage, slot_stride, stage_stride, stage_dtype, world, sa, sw, bias, outs, n_out, c_dtype,
+                        c_stride, rows, N, row0, nullptr, nullptr, 0);
+}
+
+int h3b_reduce_dequant_gated(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride, int stage_dtype,
+                             int world, const float *sa, const float *sw, const float *bias, float *X, int64_t c_stride,
+                             int rows, int N, int row0, const uint8_t *rtype, const float *gate, int64_t g_stride) {
+  if (!gate) return fail("reduce_dequant (gated): null gate table");
+  void *outs[1] = {X};
+  return reduce_enqueue(ctx, stage, slot_stride, stage_stride, stage_dtype, world, sa, sw, bias, outs, 1, H3B_F32, c_stride,
+                        rows, N, row0, rtype, gate, g_stride);
 }
 
 // ---- the product with a LoRA term for callers that cannot allocate ------------------------------------------------

@@ -59,6 +59,12 @@ struct ReduceLaunch {
   int n_out;
   long long c_stride;
   int c_dtype, rows, N, row0;
+  // Gated-residual epilogue (the reference's epilogue 1, kernels/gemm.metal:18-20,256-259) on the owner's rows:
+  // out[0] is the fp32 residual stream X and X[row0 + m][n] += gate[rtype[m]][n] * v. rtype points at the owner's
+  // first row. gate == null: plain store.
+  const unsigned char *rtype;
+  const float *gate;
+  long long g_stride;
 };
 cudaError_t launch_reduce_dequant(const ReduceLaunch &r, int sms, cudaStream_t stream);
 

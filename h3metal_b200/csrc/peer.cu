@@ -141,6 +141,19 @@ __global__ void __launch_bounds__(256) reduce_dequant_kernel(const __grid_consta
       for (int j = 0; j < 8; ++j) v[j] = __fadd_rn(v[j], b[j]);
     }
     const long long dst = (static_cast<long long>(r.row0) + m) * r.c_stride + n;
+    if constexpr (sizeof(OUT_T) == 4) {
+      if (r.gate != nullptr) {  // X += gate[type] * v: one multiply, one add, like the product's own epilogue 1
+        float *x = static_cast<float *>(r.out[0]) + dst;
+        const float *gr = r.gate + static_cast<long long>(r.rtype[m]) * r.g_stride + n;
+        const float4 x0 = *reinterpret_cast<const float4 *>(x), x1 = *reinterpret_cast<const float4 *>(x + 4);
+        const float4 g0 = *reinterpret_cast<const float4 *>(gr), g1 = *reinterpret_cast<const float4 *>(gr + 4);
+        reinterpret_cast<float4 *>(x)[0] = make_float4(__fadd_rn(x0.x, __fmul_rn(g0.x, v[0])), __fadd_rn(x0.y, __fmul_rn(g0.y, v[1])),
+                                                       __fadd_rn(x0.z, __fmul_rn(g0.z, v[2])), __fadd_rn(x0.w, __fmul_rn(g0.w, v[3])));
+        reinterpret_cast<float4 *>(x)[1] = make_float4(__fadd_rn(x1.x, __fmul_rn(g1.x, v[4])), __fadd_rn(x1.y, __fmul_rn(g1.y, v[5])),
+                                                       __fadd_rn(x1.z, __fmul_rn(g1.z, v[6])), __fadd_rn(x1.w, __fmul_rn(g1.w, v[7])));
+        continue;
+      }
+    }
 #pragma unroll
     for (int o = 0; o < kMaxPeers; ++o) {
       if (o < r.n_out) store8(static_cast<OUT_T *>(r.out[o]) + dst, v);
@@ -168,6 +181,7 @@ cudaError_t launch_peer_sync(const PeerSync &p, cudaStream_t stream) {
 
 cudaError_t launch_reduce_dequant(const ReduceLaunch &r, int sms, cudaStream_t stream) {
   if (r.stage_dtype != kDtypeI32 && r.stage_dtype != kDtypeBf16) return cudaErrorInvalidValue;
+  if (r.gate != nullptr && (r.c_dtype != kDtypeF32 || r.n_out != 1 || r.rtype == nullptr)) return cudaErrorInvalidValue;
   switch (r.c_dtype) {
     case kDtypeBf16: return launch_typed<__nv_bfloat16>(r, sms, stream);
     case kDtypeF16: return launch_typed<__half>(r, sms, stream);

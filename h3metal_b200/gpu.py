@@ -81,6 +81,7 @@ def _signatures():
         "h3b_gemm_w8a8_push": (i32, [vp, vp, i64, vp, i64, vp, vp, ctypes.POINTER(vp), i32, i32, i32, i64, i32, i32, i32]),
         "h3b_reduce_dequant": (i32, [vp, vp, i64, i64, i32, i32, vp, vp, vp, ctypes.POINTER(vp), i32, i32, i64, i32, i32,
                                      i32]),
+        "h3b_reduce_dequant_gated": (i32, [vp, vp, i64, i64, i32, i32, vp, vp, vp, vp, i64, i32, i32, i32, vp, vp, i64]),
         "h3b_gemm_tile_n": (i32, [vp, i32, i32]),
         "h3b_gemm_set_policy": (i32, [vp, i32, i32, i32]),
         "h3b_rot_set_policy": (i32, [vp, i32, i32, i32]),
@@ -417,6 +418,17 @@ class Gpu:
                                               c_stride, rows, N, row0))
         if self._profile:
             self.names.append("reduce_dequant")
+
+    def reduce_dequant_gated_native(self, stage_ptr: int, slot_stride: int, stage_stride: int, stage_dtype: str, world: int,
+                                    sa_ptr: int | None, sw: Tensor | None, bias: Tensor | None, x: Tensor, c_stride: int,
+                                    rows: int, N: int, row0: int, rtype_ptr: int, gate: Tensor, g_stride: int):
+        p = lambda t: t.ptr if t is not None else None  # noqa: E731
+        self._check(lib().h3b_reduce_dequant_gated(self.ctx, ctypes.c_void_p(stage_ptr), slot_stride, stage_stride,
+                                                    _ABI_DTYPE[stage_dtype], world,
+                                                    ctypes.c_void_p(sa_ptr) if sa_ptr else None, p(sw), p(bias), x.ptr,
+                                                    c_stride, rows, N, row0, ctypes.c_void_p(rtype_ptr), gate.ptr, g_stride))
+        if self._profile:
+            self.names.append("reduce_dequant(epi1)")
 
     def gemm_tile_n(self, N: int, lora: bool) -> int:
         return lib().h3b_gemm_tile_n(self.ctx, N, int(lora))

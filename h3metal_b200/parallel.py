@@ -235,14 +235,8 @@ class RowParallelLinear:
     def __call__(self, x_local: Tensor, x_stride: int | None = None) -> Tensor:
         dist = _dist()
         gpu, wt, M = self.gpu, self.wt, self.M
-        D = wt.K
-        stride = x_stride or (2 * D if self.swiglu_in else D)
-        mode = 1 if self.swiglu_in else 0
         # (1)-(3): one scale per token over the WHOLE row
-        gpu.rot_amax_native(x_local, stride, self.sa, M, D, self.block, mode)
-        if self.world > 1:
-            dist.all_reduce(self.sa.torch(), op=dist.ReduceOp.MAX, group=self.group)
-        gpu.rot_q8_given_amax_native(x_local, stride, self.a8, self.sa, M, D, self.block, mode)
+        self._quantise(x_local, x_stride)
         # (4)-(6)
         if self.push:
             return self._push(gpu, wt)
@@ -273,7 +267,30 @@ class RowParallelLinear:
         return self.out
 
 
-    def _push(self, gpu: Gpu, wt: ops.QWeight) -> Tensor:
+    def accumulate_gated(self, x_local: Tensor, X: Tensor, rtype: Tensor, gate: Tensor, g_stride: int,
+                         x_stride: int | None = None) -> Tensor:
+        """The layer with the reference's second epilogue (ops.gemm(..., epi=1), h3metal/ops.py:124-174): instead of
+        returning the output, X[m][n] += gate[rtype[m]][n] * y[m][n] on THIS rank's M / p rows of the fp32 residual
+        stream. X fp32 [rows][N] and rtype u8 [rows] hold the rank's own rows; gate fp32 [types][g_stride]. Push
+        variants only (every rank finishes its own rows)."""
+        if not self.push:
+            raise ValueError("accumulate_gated needs reduce='push' or 'push_bf16'")
+        return self._push(self.gpu, self.wt, x_local, x_stride, gated=(X, rtype, gate, g_stride))
+
+    def _quantise(self, x_local: Tensor, x_stride: int | None):
+        dist = _dist()
+        gpu, D = self.gpu, self.wt.K
+        stride = x_stride or (2 * D if self.swiglu_in else D)
+        mode = 1 if self.swiglu_in else 0
+        gpu.rot_amax_native(x_local, stride, self.sa, self.M, D, self.block, mode)
+        if self.world > 1:
+            dist.all_reduce(self.sa.torch(), op=dist.ReduceOp.MAX, group=self.group)
+        gpu.rot_q8_given_amax_native(x_local, stride, self.a8, self.sa, self.M, D, self.block, mode)
+
+    def _push(self, gpu: Gpu, wt: ops.QWeight, x_local: Tensor | None = None, x_stride: int | None = None,
+              gated=None) -> Tensor:
+        if x_local is not None:
+            self._quantise(x_local, x_stride)
         mem, N = self.block_mem, wt.N
         buf = (self.calls % 2) * self.stage_bytes  # calls alternate between the two staging buffers
         self.calls += 1
@@ -283,6 +300,12 @@ class RowParallelLinear:
                              self.m_pad, N, wt.K)
         mem.sync()  # every rank's partials of my rows have landed
         esize = 4 if self.stage_dtype == "i32" else 2
+        if gated is not None:
+            X, rtype, gate, g_stride = gated
+            gpu.reduce_dequant_gated_native(mem.addr(self.rank, buf), self.slot_bytes // esize, N, self.stage_dtype,
+                                            self.world, self.sa.ptr + 4 * self.r0, wt.sw, self.bias, X, N, self.rows, N, 0,
+                                            rtype.ptr, gate, g_stride)
+            return X
         outs = [self.out.ptr] if self.scatter else [mem.addr(q, self.out_offset) for q in range(self.world)]
         gpu.reduce_dequant_native(mem.addr(self.rank, buf), self.slot_bytes // esize, N, self.stage_dtype, self.world,
                                   self.sa.ptr + 4 * self.r0, wt.sw, self.bias, outs, self.out.dtype, N, self.rows, N,

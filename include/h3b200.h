@@ -190,6 +190,15 @@ H3B_API int h3b_gemm_w8a8_push(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, 
 H3B_API int h3b_reduce_dequant(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride,
                                int stage_dtype, int world, const float *sa, const float *sw, const float *bias,
                                void *const *outs, int n_out, int c_dtype, int64_t c_stride, int rows, int N, int row0);
+/* The owner's reduction with the reference's second epilogue (EPI 1, kernels/gemm.metal:18-20,256-259), for the
+ * attention-out and FFN-down projections of models that accumulate into an fp32 residual stream: with v the value
+ * h3b_reduce_dequant would store,  X[row0 + m][n] += gate[rtype[m]][n] * v  for the owner's rows; X fp32
+ * [..][c_stride] local to the owner (every GPU keeps its own rows of the stream), rtype one byte per owned row, gate
+ * fp32 [types][g_stride]. Bit-identical to h3b_gemm_w8a8_gated on one GPU for int32 staging. */
+H3B_API int h3b_reduce_dequant_gated(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride,
+                                     int stage_dtype, int world, const float *sa, const float *sw, const float *bias,
+                                     float *X, int64_t c_stride, int rows, int N, int row0, const uint8_t *rtype,
+                                     const float *gate, int64_t g_stride);
 
 /* The product with a LoRA term for callers that cannot allocate device memory. It has no counterpart in the
  * reference (whose Scratch object, h3metal/ops.py:37-47, simply grows a buffer on demand).

@@ -214,25 +214,38 @@ class SharedPeerGpu(OracleBackedGpu):
                                          sw.numpy().reshape(-1)[:N], None)
                 self._bytes(slot, part.size * 2).view(np.uint16).reshape(part.shape)[...] = gemm_ref.store_as(v, "bf16")
 
+    def reduce_dequant_gated_native(self, stage_ptr, slot_stride, stage_stride, stage_dtype, world, sa_ptr, sw, bias, x,
+                                    c_stride, rows, N, row0, rtype_ptr, gate, g_stride):
+        from oracle import gemm_ref
+        v = self._reduced(stage_ptr, stage_dtype, world, sa_ptr, sw, bias, rows, N)
+        X = x.numpy().reshape(-1)[:rows * N].reshape(rows, N)
+        types = self._bytes(rtype_ptr, rows)
+        table = gate.numpy().reshape(-1, g_stride)[:, :N]
+        X[...] = gemm_ref.accumulate_gated(X, v, table, types)
+
     def reduce_dequant_native(self, stage_ptr, slot_stride, stage_stride, stage_dtype, world, sa_ptr, sw, bias, outs,
                               out_dtype, c_stride, rows, N, row0=0):
-        from oracle import bf16_bits_to_f32, gemm_ref
+        from oracle import gemm_ref
         assert stage_stride == N and c_stride == N and slot_stride == rows * N
-        esize = 4 if stage_dtype == "i32" else 2
-        stage = self._bytes(stage_ptr, world * rows * N * esize)
-        b = bias.numpy().reshape(-1)[:N] if bias is not None else None
-        if stage_dtype == "i32":
-            acc = stage.view(np.int32).reshape(world, rows, N).sum(axis=0, dtype=np.int32)
-            v = gemm_ref.epilogue_q8(acc, self._bytes(sa_ptr, rows * 4).view(np.float32), sw.numpy().reshape(-1)[:N], b)
-        else:
-            parts = bf16_bits_to_f32(stage.view(np.uint16).reshape(world, rows, N))
-            v = np.zeros((rows, N), np.float32)
-            for s in range(world):
-                v = (v + parts[s]).astype(np.float32)
-            if b is not None:
-                v = (v + b[None, :]).astype(np.float32)
+        v = self._reduced(stage_ptr, stage_dtype, world, sa_ptr, sw, bias, rows, N)
         bits = gemm_ref.store_as(v, out_dtype)
         osize = gpu_mod._SIZE[out_dtype]
         for o in outs:
             dst = self._bytes(o + row0 * N * osize, rows * N * osize)
             dst.view(gpu_mod._NP[out_dtype]).reshape(rows, N)[...] = bits
+
+    def _reduced(self, stage_ptr, stage_dtype, world, sa_ptr, sw, bias, rows, N):
+        from oracle import bf16_bits_to_f32, gemm_ref
+        esize = 4 if stage_dtype == "i32" else 2
+        stage = self._bytes(stage_ptr, world * rows * N * esize)
+        b = bias.numpy().reshape(-1)[:N] if bias is not None else None
+        if stage_dtype == "i32":
+            acc = stage.view(np.int32).reshape(world, rows, N).sum(axis=0, dtype=np.int32)
+            return gemm_ref.epilogue_q8(acc, self._bytes(sa_ptr, rows * 4).view(np.float32), sw.numpy().reshape(-1)[:N], b)
+        parts = bf16_bits_to_f32(stage.view(np.uint16).reshape(world, rows, N))
+        v = np.zeros((rows, N), np.float32)
+        for s in range(world):
+            v = (v + parts[s]).astype(np.float32)
+        if b is not None:
+            v = (v + b[None, :]).astype(np.float32)
+        return v

@@ -26,7 +26,7 @@ rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 g = Gpu(device=rank)
-M, D, F, B = 512, 1024, 2048, 128
+M, D, F, B = 1024, 1024, 2048, 128
 rng = np.random.default_rng(5)
 x = oracle.bf16_round_bits((rng.standard_normal((M, D)) * 2).astype(np.float32))
 w_up = rng.integers(-127, 128, size=(2 * F, D), dtype=np.int8); s_up = rng.uniform(1e-3, 2e-3, size=2 * F).astype(np.float32)
@@ -66,12 +66,26 @@ for reduce, scatter in (("int32", True), ("push", False), ("push", True), ("push
         else:
             assert np.array_equal(yp.numpy(), want), (reduce, scatter, call)
     layer.close()
+# the same layer accumulating into this rank's rows of an fp32 residual stream (the reference's epilogue 1)
+rows = M // world
+rng2 = np.random.default_rng(77)
+x_stream = rng2.standard_normal((M, D)).astype(np.float32)
+types = rng2.integers(0, 3, size=M).astype(np.uint8)
+gates = rng2.standard_normal((3, D)).astype(np.float32)
+X1 = g.upload(x_stream)
+ops.gemm(g, a8b, full_dn, X1, M, sa=sab, epi=1, rtype=g.upload(types), gate=g.upload(gates), g_stride=D, tile=(128, 32, 4))
+layer = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=B, swiglu_in=True, reduce="push", scatter=True)
+X = g.upload(x_stream[r0:r0 + rows])
+layer.accumulate_gated(h_local, X, g.upload(types[r0:r0 + rows]), g.upload(gates), D)
+g.wait()
+assert np.array_equal(X.numpy(), X1.numpy()[r0:r0 + rows]), "gated accumulate on the owner's rows"
+layer.close()
 dist.barrier(); dist.destroy_process_group()
 print(f"rank {rank} ok")
 '''
 
 
-@pytest.mark.parametrize("world", [1, 2])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_sharded_layers_match_one_gpu_bit_for_bit(tmp_path, world):
     import torch
     if torch.cuda.device_count() < world:

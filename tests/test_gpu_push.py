@@ -94,6 +94,39 @@ def test_int32_slots_hold_the_partial_accumulators(gpu):
         gpu.peer_free(b.ptr)
 
 
+def test_gated_reduction_matches_the_single_gpu_gated_product(gpu):
+    """Owner-side reduction with the reference's epilogue 1: bit-identical to h3b_gemm_w8a8_gated on the whole K."""
+    world, M, N, K = 2, 512, 768, 1024
+    rng = np.random.default_rng(17)
+    a, w, sa, sw, bias = _case(rng, M, N, K)
+    x0 = rng.standard_normal((M, N)).astype(np.float32)
+    types = rng.integers(0, 4, size=M).astype(np.uint8)
+    gates = rng.standard_normal((4, N)).astype(np.float32)
+    d_sa, d_sw, d_bias, d_gate, d_types = gpu.upload(sa), gpu.upload(sw), gpu.upload(bias), gpu.upload(gates), gpu.upload(types)
+    want = gpu.upload(x0)
+    gpu.gemm_gated_native(gpu.upload(a), K, gpu.upload(w), K, d_sw, d_sa, d_bias, want, N, M, N, K, d_types, d_gate, N)
+    rows, kp = M // world, K // world
+    blocks = [gpu.peer_alloc(world * rows * N * 4) for _ in range(world)]
+    for r in range(world):
+        slots = [blocks[o].ptr + r * rows * N * 4 for o in range(world)]
+        gpu.gemm_push_native(gpu.upload(np.ascontiguousarray(a[:, r * kp:(r + 1) * kp])), kp,
+                             gpu.upload(np.ascontiguousarray(w[:, r * kp:(r + 1) * kp])), kp, d_sw, d_sa, slots, rows, "i32",
+                             N, M, N, kp)
+    got = []
+    for o in range(world):
+        X = gpu.upload(x0[o * rows:(o + 1) * rows])
+        gpu.reduce_dequant_gated_native(blocks[o].ptr, rows * N, N, "i32", world, d_sa.ptr + 4 * o * rows, d_sw, d_bias, X, N,
+                                        rows, N, 0, d_types.ptr + o * rows, d_gate, N)
+        got.append(X)
+    gpu.wait()
+    from oracle import gemm_ref
+    ref = gemm_ref.accumulate_gated(x0, gemm_ref.epilogue_q8(gemm_ref.int32_product(a, w), sa, sw, bias), gates, types)
+    assert np.array_equal(want.numpy(), ref)
+    assert np.array_equal(np.concatenate([x.numpy() for x in got]), ref)
+    for b in blocks:
+        gpu.peer_free(b.ptr)
+
+
 def test_rendezvous_gives_up_when_a_rank_never_signals(gpu):
     """A wait for a flag nobody sets must run out (about a second), surface at wait() and leave the context usable."""
     from h3metal_b200.gpu import GpuError

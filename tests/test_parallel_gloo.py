@@ -82,12 +82,23 @@ def _worker(rank, port, results):
             assert all(np.array_equal(o, outs[0]) for o in outs)
             pushed[(reduce, scatter)] = outs[0]
             layer.close()
+        # the same layer accumulating into this rank's rows of an fp32 residual stream (the reference's epilogue 1)
+        rows = M // WORLD
+        rng2 = np.random.default_rng(99)
+        x_stream = rng2.standard_normal((M, D)).astype(np.float32)
+        types = rng2.integers(0, 3, size=M).astype(np.uint8)
+        gates = rng2.standard_normal((3, D)).astype(np.float32)
+        layer = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True, reduce="push", scatter=True)
+        X = g.upload(x_stream[rank * rows:(rank + 1) * rows])
+        layer.accumulate_gated(h_local, X, g.upload(types[rank * rows:(rank + 1) * rows]), g.upload(gates), D)
+        gated = X.numpy().copy()
+        layer.close()
         tok = parallel.TokenShardedLinear(g, None, parallel.ops.QWeight("q8", g.upload(w_up), g.upload(s_up), 2 * F, D,
                                                                          bias=g.upload(b_up)), M, block=BLOCK)
         h_tok = tok(g.upload(x[tok.m0:tok.m0 + tok.rows], "bf16"))
         results[rank] = dict(slices=up.slices, h_local=h_local.numpy().copy(), a8=down.a8.numpy().copy(),
                              sa=down.sa.numpy().copy(), y=y.numpy().copy(), y_rows=(down_rs.r0, y_rows.numpy().copy()), y_fast=y_fast.numpy().copy(),
-                             tok=(tok.m0, tok.rows, h_tok.numpy().copy()), pushed=pushed)
+                             tok=(tok.m0, tok.rows, h_tok.numpy().copy()), pushed=pushed, gated=gated)
     finally:
         dist.destroy_process_group()
 
@@ -124,6 +135,15 @@ def test_two_ranks_reproduce_one_rank_bit_for_bit():
             else:
                 a, b = oracle.bf16_bits_to_f32(got).astype(np.float64), oracle.bf16_bits_to_f32(want_rows).astype(np.float64)
                 assert np.linalg.norm(a - b) / np.linalg.norm(b) <= 5e-3, (reduce, scatter)
+        # gated accumulate on the rank's own rows: X += gate[type] * (product + bias), fp32, from the exact int32 sum
+        rng2 = np.random.default_rng(99)
+        x_stream = rng2.standard_normal((M, D)).astype(np.float32)
+        types = rng2.integers(0, 3, size=M).astype(np.uint8)
+        gates = rng2.standard_normal((3, D)).astype(np.float32)
+        acc = gemm_ref.int32_product(q2, _inputs()[2][0])
+        v = gemm_ref.epilogue_q8(acc, s2, _inputs()[2][1], _inputs()[2][2])
+        want_x = gemm_ref.accumulate_gated(x_stream, v, gates, types)
+        assert np.array_equal(r["gated"], want_x[r0:r0 + M // WORLD])
         # token-sharded: rows of the full result
         m0, rows, h_tok = r["tok"]
         assert (m0, rows) == (rank * M // WORLD, M // WORLD) and np.array_equal(h_tok, h[m0:m0 + rows])
