@@ -227,6 +227,7 @@ class Gpu:
         self.max_buffer = lib().h3b_max_buffer_length(self.ctx)
         self.sm_count = lib().h3b_sm_count(self.ctx)
         self.rot_block = 256  # rotation block used when rot_q8 is launched through the generic launch()
+        self.lora_t_split = 4  # ops.gemm may split K of a LoRA term's input-side product this many ways (0 = never)
         self._kernels = {}
         self.names = []
         self.use_stream(None)

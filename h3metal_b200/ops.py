@@ -52,6 +52,13 @@ class Scratch:
             self.t = self.gpu.empty((self.n,), "f16")
         return self.t.view((rows, cols))
 
+    def get_i32(self, rows: int, cols: int) -> Tensor:
+        """A second, int32 buffer: partial accumulators of T when its product is split along K."""
+        if rows * cols > getattr(self, "n32", 0):
+            self.n32 = rows * cols
+            self.t32 = self.gpu.empty((self.n32,), "i32")
+        return self.t32.view((rows, cols))
+
 
 LOW_TILE = (64, 32, 2)  # the input-side product's tile in the reference: R is a multiple of 32
 RANK_STEP = 16          # rank ranges start and end on multiples of this (the fp16 MMA's K granularity)
@@ -69,10 +76,22 @@ class LowRank:
     hi: np.ndarray
     scratch: Scratch
     tables: dict = field(default_factory=dict)
+    codes: np.ndarray | None = None  # host copy of a's int8 codes [R][K], for the K-split layout
+    splits: dict = field(default_factory=dict)
 
     @property
     def R(self) -> int:
         return self.a.N
+
+    def split_major(self, gpu: Gpu, S: int) -> Tensor:
+        """a's codes laid out [S][R][K / S]: slice s of every rank's K, contiguous, so that one product of the
+        activations seen as [M * S][K / S] with this as [S * R][K / S] yields all S partial sums of T at once."""
+        t = self.splits.get(S)
+        if t is None:
+            R, K = self.codes.shape
+            t = gpu.upload(np.ascontiguousarray(self.codes.reshape(R, S, K // S).transpose(1, 0, 2)))
+            self.splits[S] = t
+        return t
 
     def table(self, gpu: Gpu, tn: int) -> Tensor:
         """int32 [T's row stride, B's row stride, then (k0, k1) per column tile of width tn]. A last, partial tile
@@ -119,7 +138,21 @@ def low_rank(gpu: Gpu, A: np.ndarray, B: np.ndarray, scratch: Scratch, act: str 
     any_used = used.any(1)
     lo = np.where(any_used, used.argmax(1), 0).astype(np.int64)
     hi = np.where(any_used, R - used[:, ::-1].argmax(1), 0).astype(np.int64)
-    return LowRank(aw, gpu.upload(b), lo, hi, scratch)
+    return LowRank(aw, gpu.upload(b), lo, hi, scratch, codes=codes)
+
+
+def _t_split(gpu, lo: LowRank, m_rows: int, K: int, a_stride) -> int:
+    """How many ways to split K in T's product: 1 unless the GPU asks for it (`gpu.lora_t_split`, the real Gpu's
+    default), the activations are contiguous and the unsplit product would use at most half of the SMs."""
+    want = getattr(gpu, "lora_t_split", 0)
+    if not want or lo.codes is None or (a_stride not in (None, K)):
+        return 1
+    tiles = m_rows // 128
+    for S in (4, 2):
+        if S <= want and tiles * S <= 2 * getattr(gpu, "sm_count", 148) and tiles * 2 <= getattr(gpu, "sm_count", 148) \
+                and K % (S * 128) == 0 and K // S >= 512:
+            return S
+    return 1
 
 
 def pad_rows(m: int, tile: int = 128) -> int:
@@ -152,7 +185,20 @@ def gemm(gpu: Gpu, a: Tensor, wt: QWeight, out: Tensor, M: int, *, sa: Tensor | 
         # T covers the rows of the whole 128-row tiles the activations are allocated in
         m_rows = (M + 127) // 128 * 128
         t = lo.scratch.get(m_rows, lo.R)
-        gemm(gpu, a, lo.a, t, m_rows, sa=sa, a_stride=a_stride, tile=LOW_TILE)
+        S = _t_split(gpu, lo, m_rows, wt.K, a_stride)
+        if S > 1:
+            # Few row tiles and a long K leave most SMs idle in T's product: split K S ways in ONE launch. The
+            # activations seen as [M * S][K / S] times a's codes as [S * R][K / S] give, in the diagonal blocks of an
+            # int32 [M * S][S * R] result, the S exact partial sums; the owner-side reduction kernel of the
+            # row-parallel layers adds them and applies T's epilogue. Same bits as the unsplit product.
+            R, kp = lo.R, wt.K // S
+            part = lo.scratch.get_i32(m_rows * S, S * R)
+            gpu.gemm_native(a.view((m_rows * S, kp)), kp, lo.split_major(gpu, S), kp, None, None, None, part, "i32", S * R,
+                            m_rows * S, S * R, kp, name=f"gemm(q8,{wt.K}->{R},T split {S})")
+            gpu.reduce_dequant_native(part.ptr, S * R + R, S * S * R, "i32", S, sa.ptr, lo.a.sw, None, [t.ptr], "f16", R,
+                                      m_rows, R)
+        else:
+            gemm(gpu, a, lo.a, t, m_rows, sa=sa, a_stride=a_stride, tile=LOW_TILE)
         _low = (t, lo)
         wt = replace(wt, low=None)
     if ksplit > 1:

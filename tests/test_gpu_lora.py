@@ -93,3 +93,25 @@ def test_term_is_not_silently_dropped(gpu):
     r = _run(gpu, rng, 128, 256, 512, A_l, B_l, "f32")
     main_only = gemm_ref.epilogue_q8(r["acc"], r["sa"], r["sw"], r["bias"])
     assert rel_fro(r["got_f"], main_only) > 0.1
+
+
+@pytest.mark.parametrize("K,expect_split", [(4096, 4), (1024, 2), (768, 1)])
+def test_k_split_of_the_input_side_product_changes_no_bit(gpu, K, expect_split):
+    """T's product split along K (one launch over the activations seen as [M * S][K / S], partial sums added exactly
+    by the reduction kernel) against the unsplit product and the oracle."""
+    rng = np.random.default_rng(K)
+    M, N, rank = 640, 512, 64
+    A_l = (rng.standard_normal((rank, K)) / np.sqrt(K)).astype(np.float32)
+    B_l = (rng.standard_normal((N, rank)) * 0.5).astype(np.float32)
+    lo = ops.low_rank(gpu, A_l, B_l, ops.Scratch(gpu))
+    assert ops._t_split(gpu, lo, M, K, None) == expect_split
+    results = []
+    for split in (4, 0):
+        gpu.lora_t_split = split
+        try:
+            r = _run(gpu, np.random.default_rng(5), M, N, K, A_l, B_l, "bf16")
+        finally:
+            gpu.lora_t_split = 4
+        assert np.array_equal(r["T"], gemm_ref.lora_T(r["a"], r["sa"], r["term"]))
+        results.append(r)
+    assert np.array_equal(results[0]["T"], results[1]["T"]) and np.array_equal(results[0]["got"], results[1]["got"])
