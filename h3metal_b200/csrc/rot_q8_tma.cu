@@ -1,5 +1,7 @@
 // Rotate + per-token int8 quantise, TMA-fed: the normal case of the path (16-bit activations, rows of up to 16384
-// channels) and the norm + modulation front end on the fp32 residual stream (rows of up to 8192 channels).
+// channels) and the norm + modulation front end on the fp32 residual stream (rows of up to 8192 channels; the
+// scale' and shift vectors of the current row type stay in shared memory and are re-fetched only when the type of a
+// CTA's next row differs).
 //
 // Same arithmetic as rot_q8.cu / norm_mod_q8.cu (the reference's kernels rot_q8, kernels/ops.metal:274-334, and
 // norm_mod_q8, :111-268, operation by operation); what differs is how rows reach the registers. Rows are fetched by
@@ -50,7 +52,8 @@ struct RotTmaArgs {
   int M, D;
   int stages;          // ring depth
   int stage_bytes;     // bytes per stage (value row, then gate row; each padded to 1024)
-  int gate_offset;     // offset of the gate row (or, norm front end, of the scale' row; the shift row follows) in a stage
+  int gate_offset;     // offset of the gate row in a stage; norm front end: distance from the scale' to the shift vector
+  int mod_bytes;       // norm front end: bytes behind the stages that hold the current row type's scale' and shift vectors
   float normaliser;
   float eps;
   int scale_mode;      // 0: scale from this row's maximum; 1: only write the maximum to sa; 2: sa holds the maximum to use
@@ -116,8 +119,10 @@ __global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const 
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t *base_ptr = smem_raw + (base - raw_addr);
-  const uint32_t tail = p.stages * p.stage_bytes;
-  const uint32_t bars = base + tail;                                       // full[kMaxStages]
+  const uint32_t mod_off = p.stages * p.stage_bytes;                       // norm front end: scale' | shift of one row type
+  const uint32_t tail = mod_off + p.mod_bytes;
+  const uint32_t bars = base + tail;                                       // full[kMaxStages], then the vectors' barrier
+  const uint32_t mod_bar = bars + 8u * kMaxStages;
   float *exchange = reinterpret_cast<float *>(base_ptr + tail + 64);       // [4][16]: row statistics, rotating buffers
   volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + tail + 320);
 
@@ -132,22 +137,23 @@ __global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const 
 
   auto issue = [&](int s, int m) {  // thread 0 only
     const uint32_t bar = bars + 8u * s;
-    mbar_arrive_expect_tx(bar, FRONT == kPlain ? row_bytes : FRONT == kSwiglu ? 2u * row_bytes : 3u * row_bytes);
+    mbar_arrive_expect_tx(bar, FRONT == kSwiglu ? 2u * row_bytes : row_bytes);
     tma_load_3d(base + s * p.stage_bytes, &p.map, bar, 0, 0, m);
     if (FRONT == kSwiglu) tma_load_3d(base + s * p.stage_bytes + p.gate_offset, &p.map, bar, 0, lines, m);
-    if (FRONT == kNorm) {
-      // the row's scale' and shift vectors ride along (from L2, where the small table lives), so that the
-      // modulation reads shared memory instead of waiting on dependent global loads
-      const int type = p.rtype[m];
-      tma_load_3d(base + s * p.stage_bytes + p.gate_offset, &p.map_mod, bar, 0, 0, type);
-      tma_load_3d(base + s * p.stage_bytes + 2 * p.gate_offset, &p.map_mod, bar, 0, lines, type);
-    }
   };
+  // Norm front end: the scale' and shift vectors of ONE row type live in shared memory behind the stages (so that
+  // the modulation reads shared memory instead of waiting on dependent global loads) and are fetched by TMA, from
+  // L2 where the small table lives, only when a row's type differs from the row before it in this CTA.
+  int cur_type = -1;        // thread 0 only
+  int next_type = 0;        // thread 0 only: type of the row this CTA takes next, read one row ahead of its use
+  uint32_t mod_loads = 0;   // thread 0 only: completed fetches (the barrier's phase)
+  bool mod_pending = false;
 
   if (tid == 0) {
     tma_prefetch_descriptor(&p.map);
     if (FRONT == kNorm) tma_prefetch_descriptor(&p.map_mod);
     for (int s = 0; s < p.stages; ++s) mbar_init(bars + 8u * s, 1);
+    mbar_init(mod_bar, 1);
     *cta_abort = 0;
     fence_barrier_init();
   }
@@ -160,6 +166,7 @@ __global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const 
       const int m = blockIdx.x + s * gridDim.x;
       if (m < p.M) issue(s, m);
     }
+    if (FRONT == kNorm && static_cast<int>(blockIdx.x) < p.M) next_type = p.rtype[blockIdx.x];
   }
 
   int it = 0;
@@ -182,7 +189,28 @@ __global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const 
   for (int m = blockIdx.x; m < p.M; m += gridDim.x, ++it) {
     const int s = it % p.stages;
     const uint32_t ph = (it / p.stages) & 1u;
-    const bool arrived = tid != 0 || mbar_wait(bars + 8u * s, ph, cta_abort, p.status, kStatusRotTimeout);
+    bool arrived = true;
+    if (tid == 0) {
+      if (FRONT == kNorm) {
+        // every thread is past the last barrier of the row before, and the vectors are read before that barrier:
+        // they may be replaced now
+        const int type = next_type;
+        if (m + static_cast<int>(gridDim.x) < p.M) next_type = p.rtype[m + gridDim.x];  // used one row from now
+        if (type != cur_type) {
+          mbar_arrive_expect_tx(mod_bar, 2u * row_bytes);
+          tma_load_3d(base + mod_off, &p.map_mod, mod_bar, 0, 0, type);
+          tma_load_3d(base + mod_off + p.gate_offset, &p.map_mod, mod_bar, 0, lines, type);
+          mod_pending = true;
+          arrived = mbar_wait(mod_bar, mod_loads & 1u, cta_abort, p.status, kStatusRotTimeout);
+          if (arrived) {
+            mod_pending = false;
+            ++mod_loads;
+            cur_type = type;
+          }
+        }
+      }
+      arrived = arrived && mbar_wait(bars + 8u * s, ph, cta_abort, p.status, kStatusRotTimeout);
+    }
     if (!__syncthreads_and(arrived)) break;
 
     const uint8_t *stage = base_ptr + s * p.stage_bytes;
@@ -213,16 +241,18 @@ __global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const 
       const float fd = static_cast<float>(p.D);
       if (LN) {
         const float mean = __fdiv_rn(cta_reduce(sum64(v, false), false), fd);
+        refill();  // the row is in registers and everybody has passed a barrier since: its stage is free
         if (active) {
 #pragma unroll
           for (int i = 0; i < CH; ++i) v[i] = __fsub_rn(v[i], mean);
         }
       }
       const float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(cta_reduce(sum64(v, true), false), fd), p.eps));
+      refill();
       if (active) {
         float sc[CH], sh[CH];
-        read_chunk<2, CH>(stage + p.gate_offset, tid, sc);
-        read_chunk<2, CH>(stage + 2 * p.gate_offset, tid, sh);
+        read_chunk<2, CH>(base_ptr + mod_off, tid, sc);
+        read_chunk<2, CH>(base_ptr + mod_off + p.gate_offset, tid, sh);
         const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
         for (int i = 0; i < CH; i += 2) {
@@ -231,9 +261,9 @@ __global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const 
           v[i] = x.x; v[i + 1] = x.y;
         }
       }
-      if (OUT == kOutF32 || OUT == kOutF16) {  // no further exchange follows: free the stage with a barrier of its own
+      if (OUT == kOutF32 || OUT == kOutF16) {
+        // no further exchange follows: a barrier of its own before the next row may replace the vectors
         __syncthreads();
-        refill();
       }
     }
 
@@ -305,6 +335,10 @@ __global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const 
   }
 
   if (*cta_abort && tid == 0) {
+    if (FRONT == kNorm && mod_pending) {
+      int ignore = 0;
+      mbar_wait(mod_bar, mod_loads & 1u, &ignore, p.status, kStatusDrainTimeout, kDrainLimitCycles);
+    }
     // wind-down after a timeout: rows it .. it + stages - 1 may still be landing in shared memory
     for (int j = it; j < it + p.stages; ++j) {
       if (blockIdx.x + static_cast<long long>(j) * gridDim.x >= p.M) break;
@@ -371,15 +405,16 @@ cudaError_t launch_norm(const RotTmaArgs &a, int threads, size_t smem, int sms, 
 void plan(int D, int esize, bool gates, int stages_wanted, int chunk, RotTmaArgs *a, int *threads, size_t *smem) {
   const int row = (D * esize + 1023) / 1024 * 1024;
   a->gate_offset = row;
-  a->stage_bytes = esize == 4 ? 3 * row : gates ? 2 * row : row;  // fp32 rows carry their scale' and shift vectors
-  // measured: one row ahead (2 stages) is best for plain 16-bit rows; with gates, or with fp32 rows, a stage is
-  // twice as large and a single stage, which lets more CTAs share an SM, wins
+  a->stage_bytes = gates ? 2 * row : row;
+  a->mod_bytes = esize == 4 ? 2 * row : 0;  // norm front end: one row type's scale' and shift vectors
+  // measured: one row ahead (2 stages) is best for plain 16-bit rows; with gates, or with fp32 rows and their
+  // vectors, a CTA's footprint is large and a single stage, which lets more CTAs share an SM, wins
   int s = stages_wanted > 0 ? stages_wanted : ((gates || esize == 4) ? 1 : 2);
   if (s > kMaxStages) s = kMaxStages;
-  while (s > 1 && static_cast<size_t>(s) * a->stage_bytes + 2048 > 232448) --s;
+  while (s > 1 && static_cast<size_t>(s) * a->stage_bytes + a->mod_bytes + 2048 > 232448) --s;
   a->stages = s;
   *threads = (D / chunk + 31) / 32 * 32;
-  *smem = 1024 + static_cast<size_t>(s) * a->stage_bytes + 512;
+  *smem = 1024 + static_cast<size_t>(s) * a->stage_bytes + a->mod_bytes + 512;
 }
 
 }  // namespace
