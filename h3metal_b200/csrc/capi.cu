@@ -286,8 +286,10 @@ int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target, int tma_stages, int chu
 }
 
 static int rot_enqueue(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, float *sa, int M, int D,
-                       int block, int mode, int out_hr, int scale_mode) {
+                       int block, int mode, int out_hr, int scale_mode, const h3b::RotShardArgs *shard = nullptr) {
   if (!ctx) return fail("null context");
+  if (shard && !(ctx->rot_stages >= 0 && h3b::rot_q8_tma_supported(x_dtype, D)))
+    return fail("rot_q8: row maxima through peer memory need 16-bit inputs of at most 16384 channels");
   if (!x || (!out && scale_mode != 1) || (!out_hr && !sa)) return fail("rot_q8: null tensor argument");
   if (scale_mode < 0 || scale_mode > 2 || (scale_mode && out_hr)) return fail("rot_q8: bad scale mode");
   if (M <= 0 || D <= 0) return fail("rot_q8: M and D must be positive");
@@ -310,7 +312,7 @@ static int rot_enqueue(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_strid
     if (ctx->before_launch(&ps)) return -1;
     const cudaError_t e = h3b::launch_rot_q8_tma(*map, x_dtype, out, sa, M, D, block, mode, out_hr, scale_mode, ctx->rot_stages,
                                                  ctx->rot_chunk, ctx->prop.multiProcessorCount, ctx->status_dev,
-                                                 ctx->stream, ctx->overlap != 0 && !ctx->profile);
+                                                 ctx->stream, ctx->overlap != 0 && !ctx->profile, shard);
     return ctx->after_launch("rot_q8 launch", e);
   }
   int target = ctx->rot_threads > 0 ? ctx->rot_threads : 256;
@@ -338,6 +340,27 @@ int h3b_rot_amax(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, flo
 int h3b_rot_q8_given_amax(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, float *amax_to_scale,
                           int M, int D, int block, int mode) {
   return rot_enqueue(ctx, x, x_dtype, x_stride, out, amax_to_scale, M, D, block, mode, 0, 2);
+}
+
+int h3b_rot_amax_push(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, float *const *dst, int world, int M,
+                      int D, int block, int mode) {
+  if (!dst || world < 1 || world > h3b::kMaxPeers) return fail("rot_amax_push: 1 to 8 destinations");
+  h3b::RotShardArgs sh = {};
+  for (int i = 0; i < world; ++i) {
+    if (!dst[i] || reinterpret_cast<uintptr_t>(dst[i]) % 4) return fail("rot_amax_push: null or misaligned destination");
+    sh.amax_dst[i] = dst[i];
+  }
+  sh.n_dst = world; sh.amax_slots = 1; sh.scale_out = dst[0];
+  return rot_enqueue(ctx, x, x_dtype, x_stride, nullptr, dst[0], M, D, block, mode, 0, 1, &sh);
+}
+
+int h3b_rot_q8_given_amax_slots(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out, const float *slots,
+                                int64_t slot_stride, int world, float *scale, int M, int D, int block, int mode) {
+  if (!slots || !scale || world < 1 || world > h3b::kMaxPeers || slot_stride < M)
+    return fail("rot_q8_given_amax_slots: need 1 to 8 slots of at least M maxima and a scale buffer");
+  h3b::RotShardArgs sh = {};
+  sh.n_dst = 0; sh.amax_slots = world; sh.amax_slot_stride = slot_stride; sh.scale_out = scale;
+  return rot_enqueue(ctx, x, x_dtype, x_stride, out, const_cast<float *>(slots), M, D, block, mode, 0, 2, &sh);
 }
 
 int h3b_norm_mod_q8(h3b_ctx *ctx, float *x, int64_t x_stride, const float *mod, int64_t mod_stride,

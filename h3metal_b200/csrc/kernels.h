@@ -25,10 +25,23 @@ cudaError_t launch_norm_mod_q8(float *x, long long x_stride, const float *mod, l
 // TMA-fed variant for bf16 / fp16 inputs of up to 16384 channels. `map` describes the input as
 // {64, cols / 64, M} with box {64, D / 64, 1} and 128-byte swizzle (built by the caller).
 bool rot_q8_tma_supported(int x_dtype, int D);
-// chunk_wanted: channels per thread, 32 or 64 (anything else: the default).
+// Row maxima of a K-sharded row exchanged through peer-mapped memory instead of a collective. With scale_mode 1 the
+// shard's maximum of row m is stored to amax_dst[q][m] for q < n_dst (one destination per GPU: this GPU's slot in
+// every GPU's table). With scale_mode 2 the row's maximum is the largest of sa[s * amax_slot_stride + m], s <
+// amax_slots (this GPU's table, one slot per GPU), and the scale goes to scale_out[m].
+struct RotShardArgs {
+  float *amax_dst[kMaxPeers];
+  int n_dst;
+  int amax_slots;
+  long long amax_slot_stride;
+  float *scale_out;
+};
+// chunk_wanted: channels per thread, 32 or 64 (anything else: the default). shard: null for the plain behaviour
+// (scale_mode 1 writes sa[m]; scale_mode 2 reads sa[m] and overwrites it with the scale).
 cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, float *sa, int M, int D, int block,
                               int mode, int out_hr, int scale_mode, int stages_wanted, int chunk_wanted, int sms,
-                              int *status, cudaStream_t stream, bool overlap = false);
+                              int *status, cudaStream_t stream, bool overlap = false,
+                              const RotShardArgs *shard = nullptr);
 // The norm + modulation front end on the same TMA-fed kernel: fp32 rows of up to 8192 channels, no fused residual
 // update. `map` describes x as {32 floats, D / 32, M} and `map_mod` the modulation table as
 // {32 floats, mod_stride / 32, types}, both with box {32, D / 32, 1} and 128-byte swizzle.

@@ -58,6 +58,7 @@ struct RotTmaArgs {
   float eps;
   int scale_mode;      // 0: scale from this row's maximum; 1: only write the maximum to sa; 2: sa holds the maximum to use
   int overlap;         // host side: launch with programmatic stream serialization
+  RotShardArgs shard;  // where scale_mode 1 stores the maxima and scale_mode 2 finds them (see kernels.h)
 };
 
 // CH consecutive values of the thread's chunk `t`, widened to fp32. IN: 0 bf16, 1 fp16 (a line, or half a line with
@@ -310,11 +311,14 @@ __global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const 
       for (int i = 0; i < CH; i += 2) amax = fmaxf(amax, fmaxf(fabsf(v[i]), fabsf(v[i + 1])));
       float row_max = cta_reduce(amax, true);
       refill();
-      if (p.scale_mode == 1) {  // a shard of a longer row: hand the local maximum to the caller
-        if (tid == 0) p.sa[m] = row_max;
+      if (p.scale_mode == 1) {  // a shard of a longer row: hand the local maximum to the caller (or to every GPU)
+        if (tid < p.shard.n_dst) p.shard.amax_dst[tid][m] = row_max;
         continue;
       }
-      if (p.scale_mode == 2) row_max = p.sa[m];  // the whole row's maximum, reduced over the shards
+      if (p.scale_mode == 2) {  // the whole row's maximum: already reduced over the shards, or one slot per shard
+        row_max = p.sa[m];
+        for (int sl = 1; sl < p.shard.amax_slots; ++sl) row_max = fmaxf(row_max, p.sa[sl * p.shard.amax_slot_stride + m]);
+      }
       const float scale = row_max > 0.0f ? __fdiv_rn(row_max, 127.0f) : 1.0f;
       const float rs = __fdiv_rn(1.0f, scale);
       const float2 rs2 = make_float2(rs, rs);
@@ -330,7 +334,7 @@ __global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const 
 #pragma unroll
         for (int j = 0; j < CH / 16; ++j) d4[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
       }
-      if (tid == 0) p.sa[m] = scale;
+      if (tid == 0) p.shard.scale_out[m] = scale;
     }
   }
 
@@ -426,10 +430,15 @@ bool norm_mod_q8_tma_supported(int D) { return D % kChunk == 0 && D / 32 <= 256;
 
 cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, float *sa, int M, int D, int block,
                               int mode, int out_hr, int scale_mode, int stages_wanted, int chunk_wanted, int sms,
-                              int *status, cudaStream_t stream, bool overlap) {
+                              int *status, cudaStream_t stream, bool overlap, const RotShardArgs *shard) {
   RotTmaArgs a = {};
   a.map = map; a.out = out; a.sa = sa; a.status = status; a.M = M; a.D = D; a.scale_mode = scale_mode;
   a.overlap = overlap ? 1 : 0;
+  if (shard) {
+    a.shard = *shard;
+  } else {
+    a.shard.amax_dst[0] = sa; a.shard.n_dst = 1; a.shard.amax_slots = 1; a.shard.amax_slot_stride = 0; a.shard.scale_out = sa;
+  }
   a.normaliser = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
   int threads;
   size_t smem;
@@ -458,6 +467,7 @@ cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const CUtensorMap &ma
                                    cudaStream_t stream) {
   RotTmaArgs a = {};
   a.map = map; a.map_mod = map_mod; a.out = out; a.sa = sa; a.status = status; a.M = M; a.D = D; a.scale_mode = 0;
+  a.shard.amax_dst[0] = sa; a.shard.n_dst = 1; a.shard.amax_slots = 1; a.shard.scale_out = sa;
   a.mod = mod; a.mod_stride = mod_stride; a.rtype = rtype; a.eps = eps;
   a.normaliser = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
   int threads;

@@ -65,6 +65,8 @@ def _signatures():
         "h3b_norm_mod_q8": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, ctypes.c_float, i32, i32, vp, vp]),
         "h3b_rot_amax": (i32, [vp, vp, i32, i64, vp, i32, i32, i32, i32]),
         "h3b_rot_q8_given_amax": (i32, [vp, vp, i32, i64, vp, vp, i32, i32, i32, i32]),
+        "h3b_rot_amax_push": (i32, [vp, vp, i32, i64, ctypes.POINTER(vp), i32, i32, i32, i32, i32]),
+        "h3b_rot_q8_given_amax_slots": (i32, [vp, vp, i32, i64, vp, vp, i64, i32, vp, i32, i32, i32, i32]),
         "h3b_dequant_i32": (i32, [vp, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32]),
         "h3b_gemm_w8a8": (i32, [vp, vp, i64, vp, i64, vp, vp, vp, vp, i32, i64, i32, i32, i32, vp, i64, vp, i64, i32,
                                 vp]),
@@ -325,6 +327,21 @@ class Gpu:
                                                  amax_to_scale.ptr, M, D, block, mode))
         if self._profile:
             self.names.append("rot_q8_given_amax")
+
+    def rot_amax_push_native(self, x: Tensor, x_stride: int, dst, M: int, D: int, block: int, mode: int):
+        """This shard's row maxima stored to dst[q] (an address per GPU: this GPU's slot in GPU q's table)."""
+        self._check(lib().h3b_rot_amax_push(self.ctx, x.ptr, _ABI_DTYPE[x.dtype], x_stride, self._ptr_array(dst), len(dst), M,
+                                            D, block, mode))
+        if self._profile:
+            self.names.append("rot_amax(push)")
+
+    def rot_q8_given_amax_slots_native(self, x: Tensor, x_stride: int, out: Tensor, slots_ptr: int, slot_stride: int,
+                                       world: int, scale: Tensor, M: int, D: int, block: int, mode: int):
+        self._check(lib().h3b_rot_q8_given_amax_slots(self.ctx, x.ptr, _ABI_DTYPE[x.dtype], x_stride, out.ptr,
+                                                       ctypes.c_void_p(slots_ptr), slot_stride, world, scale.ptr, M, D, block,
+                                                       mode))
+        if self._profile:
+            self.names.append("rot_q8_given_amax(slots)")
 
     def dequant_native(self, acc: Tensor, acc_stride: int, sa: Tensor, sw: Tensor, bias: Tensor | None, out: Tensor,
                        c_stride: int, M: int, N: int):

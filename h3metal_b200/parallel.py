@@ -18,7 +18,8 @@ row-parallel    W's columns (K) are split; the input arrives already sharded on 
                 `scatter=True` step (5) is a reduce-scatter and every rank finishes only its M / p rows (what a
                 following per-token operation needs; half the traffic). A faster, approximate variant all-reduces
                 dequantised fp32 or bf16 partials instead (`reduce="f32" | "bf16"`).
-                `reduce="push"` (exact) and `reduce="push_bf16"` take the communication library off the data path:
+                `reduce="push"` (exact) and `reduce="push_bf16"` take the communication library off the data path
+                (the row maxima are exchanged the same way, by peer stores into per-rank slots):
                 the product kernel stores every finished tile of its partial accumulators straight into the staging
                 memory of the GPU that owns those rows (peer stores over NVLink, overlapping the rest of the
                 product), a bounded device-side rendezvous follows, and each owner sums its M / p rows, applies the
@@ -219,7 +220,9 @@ class RowParallelLinear:
             self.rows, self.slot_bytes, self.stage_bytes, out_off, total = push_layout(
                 self.m_pad, int(N), self.world, self.stage_dtype, None if scatter else out_dtype)
             self.r0 = self.rank * self.rows
-            self.block_mem = PeerBlock(gpu, group, total)
+            # behind the staging and the output: a table of `world` slots of row maxima, for the whole-row scale
+            self.amax_offset = total
+            self.block_mem = PeerBlock(gpu, group, total + self.world * self.m_pad * 4)
             self.out_offset, self.calls = out_off, 0
             self.out = (gpu.empty((self.rows, int(N)), out_dtype) if scatter
                         else self.block_mem.view(out_off, (self.m_pad, int(N)), out_dtype))
@@ -282,6 +285,17 @@ class RowParallelLinear:
         gpu, D = self.gpu, self.wt.K
         stride = x_stride or (2 * D if self.swiglu_in else D)
         mode = 1 if self.swiglu_in else 0
+        if self.push and self.world > 1 and x_local.dtype in ("bf16", "f16") and D % 64 == 0 and D <= 16384:
+            # the maxima travel like the partial products: every rank stores its shard's maxima into its slot of
+            # every rank's table, a rendezvous, then each rank takes the largest over the slots of its own table
+            mem = self.block_mem
+            slot = self.amax_offset + self.rank * self.m_pad * 4
+            gpu.rot_amax_push_native(x_local, stride, [mem.addr(q, slot) for q in range(self.world)], self.M, D,
+                                     self.block, mode)
+            mem.sync()
+            gpu.rot_q8_given_amax_slots_native(x_local, stride, self.a8, mem.addr(self.rank, self.amax_offset), self.m_pad,
+                                               self.world, self.sa, self.M, D, self.block, mode)
+            return
         gpu.rot_amax_native(x_local, stride, self.sa, self.M, D, self.block, mode)
         if self.world > 1:
             dist.all_reduce(self.sa.torch(), op=dist.ReduceOp.MAX, group=self.group)

@@ -108,6 +108,18 @@ H3B_API int h3b_rot_amax(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_str
 H3B_API int h3b_rot_q8_given_amax(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out,
                                   float *amax_to_scale, int M, int D, int block, int mode);
 
+/* The same pair with the maxima exchanged through peer-mapped memory (h3b_peer_*) instead of a collective: every GPU
+ * has a table of `world` slots of M maxima. h3b_rot_amax_push stores this shard's maxima into dst[q][m], q < world -
+ * this GPU's slot in GPU q's table, one address per GPU (plain stores through the peer mappings). After
+ * h3b_peer_sync, h3b_rot_q8_given_amax_slots takes, for row m, the largest of slots[s * slot_stride + m], s < world
+ * (this GPU's own table), quantises the shard with it and writes the scale to scale[m]. 16-bit inputs of at most
+ * 16384 channels. Same codes and scales as the all-reduce variant. No reference counterpart. */
+H3B_API int h3b_rot_amax_push(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, float *const *dst, int world,
+                              int M, int D, int block, int mode);
+H3B_API int h3b_rot_q8_given_amax_slots(h3b_ctx *ctx, const void *x, int x_dtype, int64_t x_stride, void *out,
+                                        const float *slots, int64_t slot_stride, int world, float *scale, int M, int D,
+                                        int block, int mode);
+
 /* The product's epilogue on its own: C[m][n] = c_dtype(float(acc[m][n]) * sa[m] * sw[n] + bias[n]) for int32
  * accumulators [M][acc_stride] produced by h3b_gemm_w8a8 with H3B_I32 and summed over the GPUs of a K-sharded layer.
  * Same operation order as the fused epilogue (kernels/gemm.metal:238-255), so the result equals the single-GPU

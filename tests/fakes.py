@@ -201,6 +201,16 @@ class SharedPeerGpu(OracleBackedGpu):
                 arr.flush()
         dist.barrier(group=self.group)
 
+    def rot_amax_push_native(self, x, x_stride, dst, M, D, block, mode):
+        amax = np.abs(self._rotated(x, x_stride, M, D, block, mode)).max(axis=1).astype(np.float32)
+        for ptr in dst:
+            self._bytes(ptr, M * 4).view(np.float32)[...] = amax
+
+    def rot_q8_given_amax_slots_native(self, x, x_stride, out, slots_ptr, slot_stride, world, scale, M, D, block, mode):
+        table = self._bytes(slots_ptr, ((world - 1) * slot_stride + M) * 4).view(np.float32)
+        amax = np.max([table[s * slot_stride:s * slot_stride + M] for s in range(world)], axis=0)
+        self._quantise(self._rotated(x, x_stride, M, D, block, mode), amax.copy(), out, scale, M, D)
+
     def gemm_push_native(self, a, a_stride, w, w_stride, sw, sa, slots, rows_per_gpu, stage_dtype, stage_stride, M, N, K):
         from oracle import gemm_ref
         assert M == rows_per_gpu * len(slots) and stage_stride == N

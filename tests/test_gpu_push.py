@@ -127,6 +127,39 @@ def test_gated_reduction_matches_the_single_gpu_gated_product(gpu):
         gpu.peer_free(b.ptr)
 
 
+@pytest.mark.parametrize("world,swiglu", [(2, False), (4, True)])
+def test_row_maxima_through_slots_give_the_whole_row_scale(gpu, world, swiglu):
+    """K-sharded rotate+quantise with the maxima exchanged through per-rank slots: codes and scales of every shard
+    equal the corresponding columns of the unsharded kernel's result, bit for bit."""
+    import oracle
+    from h3metal_b200 import ops
+    M, D, block = 300, 2048, 128
+    rng = np.random.default_rng(world)
+    cols = 2 * D if swiglu else D
+    x = oracle.bf16_round_bits((rng.standard_normal((M, cols)) * 2).astype(np.float32))
+    full_q, full_s = gpu.empty((M, D), "i8"), gpu.empty((M,), "f32")
+    ops.rot_q8(gpu, gpu.upload(x, "bf16"), full_q, full_s, M, D, swiglu=swiglu, block=block)
+    dp = D // world
+    tables = [gpu.peer_alloc(world * M * 4) for _ in range(world)]  # one table of `world` slots per rank
+    shards = []
+    for r in range(world):  # value | gate columns of this rank's K shard, side by side
+        parts = [x[:, r * dp:(r + 1) * dp]] + ([x[:, D + r * dp:D + (r + 1) * dp]] if swiglu else [])
+        shards.append(gpu.upload(np.ascontiguousarray(np.concatenate(parts, axis=1)), "bf16"))
+        gpu.rot_amax_push_native(shards[r], 2 * dp if swiglu else dp, [t.ptr + r * M * 4 for t in tables], M, dp, block,
+                                 1 if swiglu else 0)
+    gpu.wait()
+    want_q, want_s = full_q.numpy(), full_s.numpy()
+    for r in range(world):
+        q, s = gpu.empty((M, dp), "i8"), gpu.empty((M,), "f32")
+        gpu.rot_q8_given_amax_slots_native(shards[r], 2 * dp if swiglu else dp, q, tables[r].ptr, M, world, s, M, dp, block,
+                                           1 if swiglu else 0)
+        gpu.wait()
+        assert np.array_equal(s.numpy(), want_s), r
+        assert np.array_equal(q.numpy(), want_q[:, r * dp:(r + 1) * dp]), r
+    for t in tables:
+        gpu.peer_free(t.ptr)
+
+
 def test_rendezvous_gives_up_when_a_rank_never_signals(gpu):
     """A wait for a flag nobody sets must run out (about a second), surface at wait() and leave the context usable."""
     from h3metal_b200.gpu import GpuError
