@@ -50,8 +50,8 @@ def measured_peaks():
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu capture
 # summarised under profiles/), keyed by workload; None until a capture exists for it.
 NCU_TRAFFIC_BYTES = {
-    # profiles/gemm_w8a8_config1_ncu.md: 531.2 MB over the step's four product launches
-    "config 1": 132.8e6,
+    # profiles/gemm_w8a8_config1_ncu.md: 538.8 MB over the step's four product launches
+    "config 1": 134.7e6,
 }
 
 
