@@ -493,6 +493,55 @@ def whole_block(args):
                       "path_share": path_s * 1e3 / ms}), flush=True)
 
 
+def sweep(args):
+    """Not the headline: the stress sweep of config 4 on one GPU. M = 66560 rows; for K in 3072 / 6144 / 16384 the
+    rotate+quantise kernel at rotation blocks 64 / 128 / 256 (GB/s of algorithmic bytes, inputs of 0.4-2.2 GB, far
+    larger than L2) and the K -> 6144 product (TOP/s). Device timing with CUDA events after warm-up; one JSON line."""
+    import torch
+    from h3metal_b200 import ops, workloads
+    from h3metal_b200.gpu import Gpu
+    gpu = Gpu(device=0)
+    dev = gpu.torch_device
+    peaks = measured_peaks()
+    M, N = 66560, 6144
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        start.record(gpu.stream)
+        for _ in range(n):
+            fn()
+        end.record(gpu.stream)
+        torch.cuda.synchronize(dev)
+        return start.elapsed_time(end) * 1e-3 / n
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4)
+    rows = []
+    for K in (3072, 6144, 16384):
+        x = gpu.wrap(workloads.activations_torch(gen, M, K, round(0.002 * K), dev))
+        a8, sa = gpu.empty((M, K), "i8"), gpu.empty((M,), "f32")
+        for block in (64, 128, 256):
+            t = timed(lambda: ops.rot_q8(gpu, x, a8, sa, M, K, block=block), 10)
+            gbs = M * (3 * K + 4) / t / 1e9
+            rows.append({"kernel": "rot_q8", "K": K, "block": block, "us": t * 1e6, "GB/s": gbs,
+                         "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]})
+        codes, scales = workloads.weight_torch(gen, N, K, dev)
+        wt = ops.QWeight("q8", gpu.wrap(codes), gpu.wrap(scales), N, K)
+        out = gpu.empty((M, N), "bf16")
+        t = timed(lambda: ops.gemm(gpu, a8, wt, out, M, sa=sa, tile=(128, 32, 4)), 5)
+        tops = 2.0 * M * N * K / t / 1e12
+        rows.append({"kernel": "gemm_w8a8", "K": K, "N": N, "us": t * 1e6, "TOP/s": tops,
+                     "frac_of_measured_int8": tops / peaks["int8_tops"], "frac_of_nominal_4500": tops / NOMINAL_INT8_TOPS})
+        del x, a8, out, wt, codes
+        torch.cuda.empty_cache()
+    gpu.wait()
+    print(json.dumps({"workload": f"config 4 sweep: M={M}, K in 3072/6144/16384, N={N}, rotation blocks 64/128/256",
+                      "peak_source": peaks["source"], "rows": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -516,6 +565,8 @@ def main():
                     help="launch the kernels with programmatic dependent launch (off by default: slower on this block)")
     ap.add_argument("--library-int8-probe", action="store_true",
                     help="time the vendor library's int8 and bf16 GEMMs on this GPU (a yardstick; runs nothing of the path)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="the K x rotation-block stress sweep of config 4 (M = 66560) instead of the block step")
     ap.add_argument("--whole-block", action="store_true",
                     help="time one whole Z-Image-shaped block with PyTorch attention (context for the path's share)")
     args = ap.parse_args()
@@ -524,6 +575,9 @@ def main():
         return
     if args.whole_block:
         whole_block(args)
+        return
+    if args.sweep:
+        sweep(args)
         return
 
     from h3metal_b200 import workloads
