@@ -112,12 +112,16 @@ class LowRank:
         return t
 
 
-def low_rank(gpu: Gpu, A: np.ndarray, B: np.ndarray, scratch: Scratch, act: str = "q8") -> LowRank:
+def low_rank(gpu: Gpu, A: np.ndarray, B: np.ndarray, scratch: Scratch, act: str = "q8", rows=None) -> LowRank:
     """The low-rank term out += x A^T B^T for x the product's input (in the stored, rotated input space).
 
     A [r][K] and B [N][r] in float. Each rank's magnitude moves from B to A (B's columns are normalised to a maximum
     of 1) so that T and B fit fp16; A is then stored as int8 with per-rank scales and applied to the same int8
-    activations as the main product. Host-side preparation, as in the reference."""
+    activations as the main product. Host-side preparation, as in the reference.
+
+    rows (not in the reference): a list of [start, stop) output ranges; the term is prepared from the WHOLE B - so
+    that the normalisation and A's codes are those of the unsharded layer - and only those rows of B' are kept, in
+    order (a GPU that holds a slice of the layer's outputs)."""
     from .quant import quant_q8
     if act != "q8":
         raise NotImplementedError("low_rank: only int8 activations (act='q8') are part of this library")
@@ -134,6 +138,8 @@ def low_rank(gpu: Gpu, A: np.ndarray, B: np.ndarray, scratch: Scratch, act: str 
     b[:, :r] = (B.astype(np.float64) / peak[None, :]).astype(np.float16)
     codes, sw = quant_q8(a)
     aw = QWeight("q8", gpu.upload(codes), gpu.upload(sw), R, K)
+    if rows is not None:
+        b = np.ascontiguousarray(np.concatenate([b[r0:r1] for r0, r1 in rows], axis=0))
     used = b != 0
     any_used = used.any(1)
     lo = np.where(any_used, used.argmax(1), 0).astype(np.int64)

@@ -172,9 +172,11 @@ class ColumnParallelLinear:
         N, K = codes.shape
         self.slices = column_slices(int(N), splits, self.rank, self.world)
         low = None
-        if lora is not None:  # (A [r][K] in the rotated input space, B [N][r]): B's rows follow the weight's
+        if lora is not None:
+            # (A [r][K] in the rotated input space, B [N][r]): the term is prepared from the whole B, so that its
+            # normalisation and A's codes are the unsharded layer's, and this rank keeps the rows of B' it owns
             A_l, B_l = lora
-            low = ops.low_rank(gpu, A_l, take_rows(B_l, self.slices), scratch or ops.Scratch(gpu))
+            low = ops.low_rank(gpu, A_l, B_l, scratch or ops.Scratch(gpu), rows=self.slices)
         self.wt = ops.QWeight("q8", _put(gpu, take_rows(codes, self.slices)), _put(gpu, take_rows(scales, self.slices)),
                               sum(b - a for a, b in self.slices), int(K),
                               bias=_put(gpu, take_rows(bias, self.slices)) if bias is not None else None, low=low)

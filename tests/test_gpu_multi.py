@@ -66,6 +66,19 @@ for reduce, scatter in (("int32", True), ("push", False), ("push", True), ("push
         else:
             assert np.array_equal(yp.numpy(), want), (reduce, scatter, call)
     layer.close()
+# column-parallel with a LoRA term (B's rows follow the weight's): this rank's columns of the single-GPU result
+A_l = (rng.standard_normal((32, D)) / np.sqrt(D)).astype(np.float32)
+B_l = (rng.standard_normal((2 * F, 32)) * 0.5).astype(np.float32)
+up_l = parallel.ColumnParallelLinear(g, None, w_up, s_up, b_up, M, block=B, splits=[F, F], lora=(A_l, B_l))
+h_lora_local = up_l(g.upload(x, "bf16"))
+full_l = ops.QWeight("q8", g.upload(w_up), g.upload(s_up), 2 * F, D, bias=g.upload(b_up),
+                     low=ops.low_rank(g, A_l, B_l, ops.Scratch(g)))
+h_lora = g.empty((M, 2 * F), "bf16")
+ops.gemm(g, a8, full_l, h_lora, M, sa=sa, tile=(128, 32, 4))
+g.wait()
+hl = h_lora.numpy()
+assert not np.array_equal(hl, hh), "the LoRA term changes the output"
+assert np.array_equal(h_lora_local.numpy(), np.concatenate([hl[:, a:b] for a, b in up_l.slices], axis=1)), "column-parallel LoRA"
 # the same layer accumulating into this rank's rows of an fp32 residual stream (the reference's epilogue 1)
 rows = M // world
 rng2 = np.random.default_rng(77)
