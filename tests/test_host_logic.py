@@ -150,3 +150,39 @@ def test_k_split_sequence_matches_the_reference():
     assert first["bias"] is not None and second["bias"] is None and first["g_stride"] == N
     with pytest.raises(ValueError):
         ops.gemm(g, a, wt, x, 100, sa=sa, epi=1, rtype=rt, gate=gate, ksplit=3)
+
+
+def test_low_rank_for_a_slice_of_the_outputs_keeps_the_whole_layers_codes(golden):
+    """rows=: the term is prepared from the whole B (same normalisation, same A' codes and scales) and only B' is cut."""
+    g = RecordingGpu()
+    full = ops.low_rank(g, golden["lr_A"], golden["lr_B"], ops.Scratch(g))
+    N = golden["lr_B"].shape[0]
+    rows = [(N // 4, N // 2), (3 * N // 4, N)]
+    part = ops.low_rank(g, golden["lr_A"], golden["lr_B"], ops.Scratch(g), rows=rows)
+    assert np.array_equal(part.a.w.numpy(), full.a.w.numpy()) and np.array_equal(part.a.sw.numpy(), full.a.sw.numpy())
+    keep = np.concatenate([np.arange(a, b) for a, b in rows])
+    assert np.array_equal(part.b.numpy(), full.b.numpy()[keep])
+    assert np.array_equal(part.lo, full.lo[keep]) and np.array_equal(part.hi, full.hi[keep])
+
+
+def test_split_of_the_input_side_product():
+    """When T's product is split along K: only if the GPU asks for it, activations are contiguous and few row tiles
+    would leave SMs idle; the split-major copy of A' holds slice s of every rank's K contiguously."""
+    rng = np.random.default_rng(0)
+    K, N, r = 4096, 256, 32
+    g = RecordingGpu()
+    lo = ops.low_rank(g, rng.standard_normal((r, K)).astype(np.float32), rng.standard_normal((N, r)).astype(np.float32),
+                      ops.Scratch(g))
+    assert ops._t_split(g, lo, 4608, K, None) == 1          # the recording stand-in does not ask for a split
+    g.lora_t_split, g.sm_count = 4, 148
+    assert ops._t_split(g, lo, 4608, K, None) == 4          # 36 row tiles
+    assert ops._t_split(g, lo, 4608, K, K) == 4
+    assert ops._t_split(g, lo, 4608, K, K + 64) == 1        # strided activations cannot be viewed as [M * S][K / S]
+    assert ops._t_split(g, lo, 17408, K, None) == 1         # 136 row tiles already fill the SMs
+    assert ops._t_split(g, lo, 4608, 1024, None) == 2       # K / 4 would be too short
+    assert ops._t_split(g, lo, 4608, 768, None) == 1
+    sm = lo.split_major(g, 4).numpy()
+    codes = lo.a.w.numpy()
+    assert sm.shape == (4, lo.R, K // 4)
+    for s in range(4):
+        assert np.array_equal(sm[s], codes[:, s * (K // 4):(s + 1) * (K // 4)])
