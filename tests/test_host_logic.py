@@ -169,7 +169,7 @@ def test_split_of_the_input_side_product():
     """When T's product is split along K: only if the GPU asks for it, activations are contiguous and few row tiles
     would leave SMs idle; the split-major copy of A' holds slice s of every rank's K contiguously."""
     rng = np.random.default_rng(0)
-    K, N, r = 4096, 256, 32
+    K, N, r = 8192, 256, 32
     g = RecordingGpu()
     lo = ops.low_rank(g, rng.standard_normal((r, K)).astype(np.float32), rng.standard_normal((N, r)).astype(np.float32),
                       ops.Scratch(g))
@@ -179,8 +179,8 @@ def test_split_of_the_input_side_product():
     assert ops._t_split(g, lo, 4608, K, K) == 4
     assert ops._t_split(g, lo, 4608, K, K + 64) == 1        # strided activations cannot be viewed as [M * S][K / S]
     assert ops._t_split(g, lo, 17408, K, None) == 1         # 136 row tiles already fill the SMs
-    assert ops._t_split(g, lo, 4608, 1024, None) == 2       # K / 4 would be too short
-    assert ops._t_split(g, lo, 4608, 768, None) == 1
+    assert ops._t_split(g, lo, 4608, 4096, None) == 2       # K / 4 would be too short to pay for a second launch
+    assert ops._t_split(g, lo, 4608, 3072, None) == 1
     sm = lo.split_major(g, 4).numpy()
     codes = lo.a.w.numpy()
     assert sm.shape == (4, lo.R, K // 4)
