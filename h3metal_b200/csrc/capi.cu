@@ -394,8 +394,8 @@ int h3b_norm_mod_q8(h3b_ctx *ctx, float *x, int64_t x_stride, const float *mod, 
     if (!mmap) return -1;
     if (ctx->before_launch(&ps)) return -1;
     const cudaError_t e = h3b::launch_norm_mod_q8_tma(map_x, *mmap, mod, mod_stride, rtype, out, sa, M, D, block, eps, ln, out_kind,
-                                                      ctx->rot_stages, ctx->prop.multiProcessorCount, ctx->status_dev,
-                                                      ctx->stream);
+                                                      ctx->rot_stages, ctx->rot_chunk, ctx->prop.multiProcessorCount,
+                                                      ctx->status_dev, ctx->stream);
     return ctx->after_launch("norm_mod_q8 launch", e);
   }
   if (ctx->before_launch(&ps)) return -1;

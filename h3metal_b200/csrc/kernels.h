@@ -48,8 +48,8 @@ cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, fl
 bool norm_mod_q8_tma_supported(int D);
 cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const CUtensorMap &map_mod, const float *mod,
                                    long long mod_stride, const unsigned char *rtype, void *out, float *sa, int M, int D,
-                                   int block, float eps, int ln, int out_kind, int stages_wanted, int sms, int *status,
-                                   cudaStream_t stream);
+                                   int block, float eps, int ln, int out_kind, int stages_wanted, int chunk_wanted, int sms,
+                                   int *status, cudaStream_t stream);
 
 // out[m][n] = c_dtype(float(acc[m][n]) * sa[m] * sw[n] + bias[n]): the product's epilogue applied to accumulators
 // that were summed elsewhere (row-parallel layers reduce their int32 partial accumulators over the GPUs first).

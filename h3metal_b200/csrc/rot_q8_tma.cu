@@ -62,14 +62,14 @@ struct RotTmaArgs {
 };
 
 // CH consecutive values of the thread's chunk `t`, widened to fp32. IN: 0 bf16, 1 fp16 (a line, or half a line with
-// CH = 32), 2 fp32 (two lines; CH = 64 only).
+// CH = 32), 2 fp32 (two lines, or one with CH = 32).
 template <int IN, int CH>
 __device__ __forceinline__ void read_chunk(const uint8_t *stage, int t, float (&v)[CH]) {
   if constexpr (IN == 2) {
-    static_assert(CH == 64, "fp32 rows are read 64 channels per thread");
+    static_assert(CH == 64 || CH == 32, "fp32 rows are read one or two lines per thread");
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int line = 2 * t + half;
+    for (int half = 0; half < CH / 32; ++half) {
+      const int line = (CH / 32) * t + half;
       const uint8_t *row = stage + line * 128;
       const int sw = line & 7;
 #pragma unroll
@@ -106,16 +106,17 @@ __device__ __forceinline__ void read_chunk(const uint8_t *stage, int t, float (&
 
 // Sum of the thread's 64 values: four interleaved partial sums, combined pairwise. With the lane tree and the
 // sequential pass over the warps below this fixes the (fp32) summation order of the row statistics.
-__device__ __forceinline__ float sum64(const float (&v)[kChunk], bool squares) {
+template <int N>
+__device__ __forceinline__ float sum64(const float (&v)[N], bool squares) {
   float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-  for (int i = 0; i < kChunk; ++i) s[i & 3] = __fadd_rn(s[i & 3], squares ? __fmul_rn(v[i], v[i]) : v[i]);
+  for (int i = 0; i < N; ++i) s[i & 3] = __fadd_rn(s[i & 3], squares ? __fmul_rn(v[i], v[i]) : v[i]);
   return __fadd_rn(__fadd_rn(s[0], s[1]), __fadd_rn(s[2], s[3]));
 }
 
 template <int IN, int BLOCK, int FRONT, bool LN, int OUT, int CH = kChunk>
 __global__ void __launch_bounds__(CH == 32 ? 512 : 256) rot_q8_tma_kernel(const __grid_constant__ RotTmaArgs p) {
-  static_assert(CH == 64 || (CH == 32 && IN != 2 && FRONT != kNorm), "half-line chunks: 16-bit inputs, no norm front end");
+  static_assert(CH == 64 || CH == 32, "a thread owns 64 or 32 channels");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -396,14 +397,19 @@ cudaError_t launch_rot(const RotTmaArgs &a, int threads, size_t smem, int sms, i
                    : launch_final<IN, BLOCK, kPlain, false, kOutQ8, CH>(a, threads, smem, sms, stream);
 }
 
-template <int BLOCK, bool LN>
-cudaError_t launch_norm(const RotTmaArgs &a, int threads, size_t smem, int sms, int out_kind, cudaStream_t stream) {
+template <int BLOCK, bool LN, int CH>
+cudaError_t launch_norm_ch(const RotTmaArgs &a, int threads, size_t smem, int sms, int out_kind, cudaStream_t stream) {
   switch (out_kind) {
-    case kOutQ8: return launch_final<2, BLOCK, kNorm, LN, kOutQ8>(a, threads, smem, sms, stream);
-    case kOutF32: return launch_final<2, BLOCK, kNorm, LN, kOutF32>(a, threads, smem, sms, stream);
-    case kOutF16: return launch_final<2, BLOCK, kNorm, LN, kOutF16>(a, threads, smem, sms, stream);
-    default: return launch_final<2, BLOCK, kNorm, LN, kOutHr>(a, threads, smem, sms, stream);
+    case kOutQ8: return launch_final<2, BLOCK, kNorm, LN, kOutQ8, CH>(a, threads, smem, sms, stream);
+    case kOutF32: return launch_final<2, BLOCK, kNorm, LN, kOutF32, CH>(a, threads, smem, sms, stream);
+    case kOutF16: return launch_final<2, BLOCK, kNorm, LN, kOutF16, CH>(a, threads, smem, sms, stream);
+    default: return launch_final<2, BLOCK, kNorm, LN, kOutHr, CH>(a, threads, smem, sms, stream);
   }
+}
+template <int BLOCK, bool LN>
+cudaError_t launch_norm(const RotTmaArgs &a, int chunk, int threads, size_t smem, int sms, int out_kind, cudaStream_t stream) {
+  return chunk == 32 ? launch_norm_ch<BLOCK, LN, 32>(a, threads, smem, sms, out_kind, stream)
+                     : launch_norm_ch<BLOCK, LN, 64>(a, threads, smem, sms, out_kind, stream);
 }
 
 void plan(int D, int esize, bool gates, int stages_wanted, int chunk, RotTmaArgs *a, int *threads, size_t *smem) {
@@ -463,8 +469,8 @@ cudaError_t launch_rot_q8_tma(const CUtensorMap &map, int x_dtype, void *out, fl
 
 cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const CUtensorMap &map_mod, const float *mod,
                                    long long mod_stride, const unsigned char *rtype, void *out, float *sa, int M, int D,
-                                   int block, float eps, int ln, int out_kind, int stages_wanted, int sms, int *status,
-                                   cudaStream_t stream) {
+                                   int block, float eps, int ln, int out_kind, int stages_wanted, int chunk_wanted, int sms,
+                                   int *status, cudaStream_t stream) {
   RotTmaArgs a = {};
   a.map = map; a.map_mod = map_mod; a.out = out; a.sa = sa; a.status = status; a.M = M; a.D = D; a.scale_mode = 0;
   a.shard.amax_dst[0] = sa; a.shard.n_dst = 1; a.shard.amax_slots = 1; a.shard.scale_out = sa;
@@ -472,12 +478,15 @@ cudaError_t launch_norm_mod_q8_tma(const CUtensorMap &map, const CUtensorMap &ma
   a.normaliser = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
   int threads;
   size_t smem;
-  plan(D, 4, false, stages_wanted, kChunk, &a, &threads, &smem);
-  if (threads > 256 || smem > 232448) return cudaErrorInvalidConfiguration;
+  // measured: 32 channels (one 128-byte line) per thread, twice the warps per SM for the same shared memory, is
+  // 12-29 % faster than 64 on this latency-bound kernel
+  const int chunk = chunk_wanted == 64 ? kChunk : 32;
+  plan(D, 4, false, stages_wanted, chunk, &a, &threads, &smem);
+  if (threads > (chunk == 32 ? 512 : 256) || smem > 232448) return cudaErrorInvalidConfiguration;
   switch (block) {
-    case 64: return ln ? launch_norm<64, true>(a, threads, smem, sms, out_kind, stream) : launch_norm<64, false>(a, threads, smem, sms, out_kind, stream);
-    case 128: return ln ? launch_norm<128, true>(a, threads, smem, sms, out_kind, stream) : launch_norm<128, false>(a, threads, smem, sms, out_kind, stream);
-    default: return ln ? launch_norm<256, true>(a, threads, smem, sms, out_kind, stream) : launch_norm<256, false>(a, threads, smem, sms, out_kind, stream);
+    case 64: return ln ? launch_norm<64, true>(a, chunk, threads, smem, sms, out_kind, stream) : launch_norm<64, false>(a, chunk, threads, smem, sms, out_kind, stream);
+    case 128: return ln ? launch_norm<128, true>(a, chunk, threads, smem, sms, out_kind, stream) : launch_norm<128, false>(a, chunk, threads, smem, sms, out_kind, stream);
+    default: return ln ? launch_norm<256, true>(a, chunk, threads, smem, sms, out_kind, stream) : launch_norm<256, false>(a, chunk, threads, smem, sms, out_kind, stream);
   }
 }
 

@@ -24,13 +24,13 @@ def _case(rng, M, D, ln, types=3):
 @pytest.mark.parametrize("M,D,ln,block", [(37, 5376, False, 256), (37, 5120, False, 256), (37, 3072, True, 256),
                                           (129, 3840, False, 128), (64, 6144, False, 128), (5, 16384, False, 64),
                                           (3, 32768, False, 256), (1, 256, True, 128), (700, 1024, True, 64)])
-@pytest.mark.parametrize("variant", ["tma", "regs"])
+@pytest.mark.parametrize("variant", ["tma", "tma_c64", "regs"])
 def test_codes_scales_and_float_outputs(gpu, request, variant, M, D, ln, block):
     """variant "tma": rows staged in shared memory by TMA (D <= 8192); "regs": the register-fed kernel."""
     rng = np.random.default_rng(1)
     x, mod, rt = _case(rng, M, D, ln)
     X, MOD, RT = gpu.upload(x), gpu.upload(mod), gpu.upload(rt)
-    gpu.set_policy(rot_stages=-1 if variant == "regs" else 0)
+    gpu.set_policy(rot_stages=-1 if variant == "regs" else 0, rot_chunk=64 if variant == "tma_c64" else 0)
     request.addfinalizer(gpu.set_policy)
     out, sa = gpu.empty((M, D), "i8"), gpu.empty((M,), "f32")
     ops.norm_mod_q8(gpu, X, MOD, RT, out, sa, M, D, eps=1e-5, ln=ln, block=block)
