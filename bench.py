@@ -1,13 +1,20 @@
-"""Benchmark of the W8A8 Hadamard-linear path: the linears of one Z-Image-Turbo-shaped DiT block (M = 4608 tokens,
-hidden 3840: QKV 3840->11520, out 3840->3840, w1|w3 3840->20480, w2 10240->3840 fed by value*silu(gate)), each
-as rotate+quantise followed by the int8 product with bias. One "step" is one pass over the four linears
-(8 kernel launches) on synthetic, seeded data.
+"""Benchmark of the W8A8 Hadamard-linear path on the linears of one DiT block: each linear is rotate+quantise followed
+by the int8 product with its epilogue. One "step" is one pass over the block's four linears on synthetic, seeded data.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 3]
 
-With N > 1 (one process per GPU under torch.distributed.run) every rank runs the block on its own M tokens
-(token sharding: the path is row-independent, no collective is needed), and `value` is the total over ranks
-divided by the slowest rank's time. Rank 0 prints ONE JSON line.
+Default workload: the 33B-class block (M = 17408 tokens, hidden 6144: QKV 6144->18432, out 6144->6144,
+w1|w3 6144->32768, w2 16384->6144 fed by value*silu(gate)).
+  N = 1   the block on one GPU.
+  N > 1   (one process per GPU under torch.distributed.run) ONE block of the same M tokens over all ranks: QKV and
+          w1|w3 column-parallel, out and w2 row-parallel with the exact int32 reduction pushed over NVLink by the
+          product kernel itself (strong scaling). Before anything is timed every rank checks a small sharded chain
+          against its own one-GPU result, bit for bit; a mismatch aborts the run.
+A second object of the same line carries the largest configuration (M = 66560, rank-64 LoRA on every linear)
+token-sharded at fixed M: every rank runs the whole block on M / N rows, no exchange.
+The timed region is repeated: R windows of exactly K steps each, every window between a barrier + synchronize on both
+sides and timed with CUDA events on the launching stream (max over ranks); `ms_per_step` is the median window.
+Rank 0 prints ONE JSON line.
 
 `--impl reference` times the reference's CPU (NumPy) arithmetic of the same path on the host cores, on a bounded
 row sample of the same workload.
@@ -32,31 +39,29 @@ if ROOT not in sys.path:
 METRIC = "dit_block_w8a8_linears_tokens_per_s"
 UNIT = "tokens/s"
 NOMINAL_INT8_TOPS = 4500.0  # B200 dense int8, datasheet
+WINDOW_SECONDS = 1.0        # the repeated windows of the headline cover at least this much GPU time
+PEER_COPY_GBS = 770.0       # measured peer copy on this pool, per direction and GPU (nominal NVLink 5: 900)
 
-
-def measured_peaks():
-    """HBM GB/s and int8 TOPS ceilings for the roofline: the pool's measured copy bandwidth and twice its measured
-    dense bf16 rate (int8 runs on the same tensor pipe at twice the bf16 rate), else the documented fallback."""
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    try:
-        with open(path) as fh:
-            p = json.load(fh)
-        return {"hbm_gbs": float(p["hbm_gbs"]), "int8_tops": 2.0 * float(p["bf16_tflops_sustained"]),
-                "source": "measured (MEASURED_PEAKS.json: hbm_gbs; 2 x bf16_tflops_sustained)"}
-    except Exception:
-        return {"hbm_gbs": 6650.0, "int8_tops": 2.0 * 1400.0, "source": "fallback (6.65 TB/s; 2 x 1.4 PFLOP/s sustained)"}
-
-
-# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the ncu capture
-# summarised under profiles/), keyed by workload; None until a capture exists for it.
+# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of
+# this benchmark's own step, averaged over the step's four product launches), keyed by config number. A figure can
+# only come from a profiler run, so it is recorded here with the capture it came from; configs without one print null.
 NCU_TRAFFIC_BYTES = {
-    # profiles/gemm_w8a8_config1_ncu.md: 538.8 MB over the step's four product launches
-    "config 1": 134.7e6,
+    1: 134.7e6,  # ncu --set full -k regex:gemm_w8a8 -s 4 -c 4, bench.py --config 1: 538.8 MB over the four launches
 }
 
 
+def hbm_peak():
+    """HBM GB/s ceiling: the pool's measured copy bandwidth, else the documented fallback."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            p = json.load(fh)
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json: hbm_gbs)", p
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s)", {}
+
+
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and throttle reasons of one GPU with nvidia-smi while timed regions run."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -64,7 +69,6 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
-        self.t_from = self.t_to = None  # host-time window whose samples count (the GPU is under load in it)
 
     def __enter__(self):
         try:
@@ -90,23 +94,25 @@ class ClockSampler:
                 self.proc.kill()
             self.thread.join(timeout=2)
 
-    def summary(self):
-        sm, mx, reasons = [], [], set()
-        for stamp, r in self.rows:
-            if len(r) < 7 or (self.t_from is not None and not (self.t_from <= stamp <= self.t_to)):
+    def summary(self, t_from=None, t_to=None):
+        """Median SM clock, largest power and the throttle reasons seen between two host times (all samples if None)."""
+        sm, mx, power, reasons = [], [], [], set()
+        for stamp, r in list(self.rows):
+            if len(r) < 7 or (t_from is not None and not (t_from <= stamp <= t_to)):
                 continue
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
+                power.append(float(r[2]))
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
-                "samples": len(sm)}
+            return {"sm_mhz": None, "sm_max_mhz": None, "power_w": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "power_w": float(np.median(power)),
+                "reasons": sorted(reasons), "samples": len(sm)}
 
 
 # ---- CPU arm: the reference's NumPy arithmetic of the path -------------------------------------------------------------
@@ -183,31 +189,206 @@ def host_threads() -> int:
     return os.cpu_count() or 1
 
 
+def config_number(cfg) -> int:
+    from h3metal_b200 import workloads
+    return next(k for k, v in workloads.CONFIGS.items() if v is cfg)
+
+
+def workload_name(cfg) -> str:
+    return (f"config {config_number(cfg)}: {cfg.name}, M={cfg.M}, " + ", ".join(f"{l.name} {l.K}->{l.N}" for l in cfg.layers)
+            + (f", rank-{cfg.lora_rank} LoRA on every linear" if cfg.lora_rank else ""))
+
+
+def cpu_sample_text(cfg, rows: int) -> str:
+    return (f"{rows} of {cfg.M} rows of every linear of the block per step (a row sample: the rate is per row and rows are "
+            f"independent): the reference's NumPy arithmetic - fp32 rotation matmul, absmax int8, float64 BLAS product, "
+            f"bias, bf16 store; weights widened to float64 once outside the timed steps")
+
+
 # ---- arms ---------------------------------------------------------------------------------------------------------
 def run_reference(args, cfg, rank, world):
     if rank != 0:
         return None
-    rows = args.cpu_rows or 512
+    rows = args.cpu_rows or (1024 if cfg.ops < 4e12 else 256)
     value, dt = time_cpu(cfg, rows, args.steps, args.warmup)
     cores = host_threads()
-    sample = (f"{rows} of {cfg.M} rows of every linear of the block per step, NumPy fp32 rotation matmul + absmax int8 + "
-              f"float64 BLAS product + bias + bf16 store, weights widened once outside the timed steps")
     return {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": workload_name(cfg), "block": cfg.block, "rows_per_step": rows},
+        "config": {"workload": workload_name(cfg), "block": cfg.block},
         "tops": value * cfg.ops / cfg.M / 1e12,
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_sample_text(cfg, rows)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
 
 
-def workload_name(cfg) -> str:
+class Timer:
+    """Windows of K calls between CUDA events on the launching stream, a barrier + synchronize on both sides of every
+    window, the maximum over ranks per window."""
+
+    def __init__(self, gpu, world):
+        import torch
+        self.torch, self.gpu, self.world, self.dev = torch, gpu, world, gpu.torch_device
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        self.torch.cuda.synchronize(self.dev)
+
+    def window(self, fn, steps, finish=None):
+        """One window; returns (milliseconds on this rank, host time at its start, host time at its end)."""
+        torch = self.torch
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        t0 = time.time()
+        start.record(self.gpu.stream)
+        for _ in range(steps):
+            fn()
+        if finish is not None:
+            finish()
+        end.record(self.gpu.stream)
+        torch.cuda.synchronize(self.dev)
+        t1 = time.time()
+        ms = start.elapsed_time(end)
+        self.barrier()
+        return ms, t0, t1
+
+    def windows(self, fn, steps, seconds=WINDOW_SECONDS, at_least=3, at_most=25, finish=None):
+        """Repeats the window until `seconds` of GPU time are covered. Returns (median ms of a window - the maximum
+        over ranks per window -, list of those maxima, [(t0, t1)] host spans of this rank's windows)."""
+        torch = self.torch
+        ms_list, spans = [], []
+        first, t0, t1 = self.window(fn, steps, finish)
+        ms_list.append(first)
+        spans.append((t0, t1))
+        # every rank must run the same number of windows: rank 0's first window decides
+        n = int(min(at_most, max(at_least, np.ceil(seconds * 1e3 / max(first, 1e-3)))))
+        if self.world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([n], device=self.dev)
+            dist.broadcast(t, 0)
+            n = int(t.item())
+        for _ in range(n - 1):
+            ms, t0, t1 = self.window(fn, steps, finish)
+            ms_list.append(ms)
+            spans.append((t0, t1))
+        if self.world > 1:
+            import torch.distributed as dist
+            t = torch.tensor(ms_list, device=self.dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_list = t.tolist()
+        return float(np.median(ms_list)), ms_list, spans
+
+
+def int8_peak_probe(gpu, clocks):
+    """The measured ceiling of the int8 tensor pipe: MMAs of the product's shape from operands resident in shared
+    memory (no TMA, no epilogue), single CTAs and CTA pairs; one launch alone (burst) and launches back to back for
+    about half a second under the power cap (sustained), with the clock and power sampled during the latter."""
+    out = {"what": "tcgen05.mma kind::i8 issue rate, operands resident in shared memory, two TMEM accumulators, "
+                   "one CTA per SM (128x256x32) or one CTA pair per two SMs (256x256x32, cta_group::2)"}
+    for name, pair in (("single", False), ("pair", True)):
+        gpu.mma_rate_probe(pair, 2000)  # warm-up (loads the kernel)
+        time.sleep(0.3)                 # let the clocks recover: the burst figure is a launch from idle
+        burst = gpu.mma_rate_probe(pair, 40000)
+        t_from = time.time()
+        runs = [gpu.mma_rate_probe(pair, 40000) for _ in range(40)]
+        t_to = time.time()
+        tail = runs[len(runs) // 2:]
+        c = clocks.summary(t_from + 0.5 * (t_to - t_from), t_to)
+        out[name] = {"burst_tops": burst["tops"], "sustained_tops": float(np.median([r["tops"] for r in tail])),
+                     "ops_per_clk_per_sm": float(np.median([r["ops_per_clk_per_sm"] for r in tail])),
+                     "ctas": burst["ctas"], "sm_mhz_sustained": c["sm_mhz"], "power_w_sustained": c["power_w"]}
+        time.sleep(0.3)
+    best = max(("single", "pair"), key=lambda k: out[k]["sustained_tops"])
+    out["peak_tops"] = out[best]["sustained_tops"]
+    out["peak_from"] = f"{best} CTAs, sustained (median of the second half of 40 launches of 11 ms back to back)"
+    return out
+
+
+def time_block(gpu, blk, cfg, M, args, timer, clocks, peak_tops=None, seconds=WINDOW_SECONDS):
+    """Windows of the whole step, then of its product launches alone and of its rotate+quantise launches alone (an
+    event pair per launch would put the launch gaps of short kernels into the figure). Returns a dict."""
+    for _ in range(max(args.warmup, 3)):
+        blk.step()
+    launches0 = gpu.launch_count
+    ms, ms_list, spans = timer.windows(blk.step, args.steps, seconds)
+    launches = (gpu.launch_count - launches0) // len(ms_list)
+    res = {"ms_per_step": ms / args.steps, "windows": len(ms_list), "window_ms": [round(x, 4) for x in ms_list],
+           "launches_per_window": int(launches),
+           "window_clocks": [clocks.summary(a, b)["sm_mhz"] for a, b in spans],
+           "clocks": clocks.summary(spans[0][0], spans[-1][1])}
+    if hasattr(blk, "gemm_only"):
+        gemm_ms, _, gspans = timer.windows(blk.gemm_only, args.steps, seconds / 2)
+        rot_ms, _, _ = timer.windows(blk.rot_only, args.steps, seconds / 4)
+        gemm_s, rot_s = gemm_ms * 1e-3, rot_ms * 1e-3
+        gemm_ops = sum(2 * l.m_pad * l.wt.K * l.wt.N for l in blk.layers) * args.steps
+        rot_bytes = sum(M * ((4 if l.swiglu_in else 2) * l.wt.K + l.wt.K + 4) for l in blk.layers) * args.steps
+        hbm, hbm_src, _ = hbm_peak()
+        tops = gemm_ops / gemm_s / 1e12
+        gc = clocks.summary(gspans[0][0], gspans[-1][1])
+        res["roofline"] = {
+            "bound": "tensor", "kernel": "gemm_w8a8_kernel (tcgen05 kind::i8)", "achieved": tops,
+            "peak": peak_tops, "unit": "TOP/s", "frac": tops / peak_tops if peak_tops else None,
+            "traffic": NCU_TRAFFIC_BYTES.get(config_number(cfg)),
+            "algorithmic_bytes": sum(l.m_pad * l.wt.K + l.wt.N * l.wt.K + 2 * l.m_pad * l.wt.N for l in blk.layers) / len(blk.layers),
+            "peak_source": "measured in this run: tcgen05 kind::i8 issue-rate probe, sustained under the power cap (int8_probe)",
+            "frac_of_nominal_4500": tops / NOMINAL_INT8_TOPS, "time_share": gemm_s / (gemm_s + rot_s),
+            "sm_mhz": gc["sm_mhz"], "power_w": gc["power_w"],
+            "ops_per_clk_per_sm": (tops * 1e12 / (gpu.sm_count * gc["sm_mhz"] * 1e6)) if gc["sm_mhz"] else None}
+        gbs = rot_bytes / rot_s / 1e9
+        res["roofline_rot_q8"] = {"bound": "hbm", "kernel": "rot_q8_tma_kernel (TMA-fed rotate + quantise)", "achieved": gbs,
+                                  "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "traffic": None, "peak_source": hbm_src,
+                                  "time_share": rot_s / (gemm_s + rot_s)}
+    return res
+
+
+def time_e2e(blk, timer, tokens_per_step, steps):
+    """The same step through the public API with HOST buffers: H2D of every input and D2H of every output inside the
+    timed region, which ends when the last download has landed."""
+    host_in, host_out = blk.host_buffers()
+    for h, x in zip(host_in, blk.inputs):
+        if h is not None:
+            h.copy_(x.torch().cpu())
+    h2d = sum(h.numel() * 2 for h in host_in if h is not None)
+    d2h = sum(h.numel() * 2 for h in host_out if h is not None)
+    step = lambda: blk.step_host(host_in, host_out)  # noqa: E731
+    for _ in range(2):
+        step()
+    blk.sync_host()
+    ms, ms_list, _ = timer.windows(step, steps, seconds=0.5, at_least=3, at_most=5, finish=blk.finish_host)
+    blk.sync_host()
+    return {"value": tokens_per_step * steps / (ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": ms / steps, "windows": len(ms_list),
+            "per_rank": "bytes are this rank's; every rank moves its own inputs and outputs"}, (host_in, host_out)
+
+
+def token_sharded_config4(gpu, args, timer, clocks, rank, world):
+    """The largest configuration at FIXED M, token-sharded: every rank runs the whole block (rank-64 LoRA on every
+    linear) on M / world rows with replicated weights; no exchange. Returns the line's second object."""
+    import torch
     from h3metal_b200 import workloads
-    number = next(k for k, v in workloads.CONFIGS.items() if v is cfg)
-    return f"config {number}: {cfg.name}, M={cfg.M}, " + ", ".join(f"{l.name} {l.K}->{l.N}" for l in cfg.layers)
+    from h3metal_b200.linear import BlockLinears
+    cfg = workloads.CONFIGS[4]
+    rows = cfg.M // world
+    blk = BlockLinears(gpu, cfg, seed=4321 + rank, M=rows)
+    steps = max(2, min(args.steps, 5))
+    for _ in range(3):
+        blk.step()
+    launches0 = gpu.launch_count
+    ms, ms_list, spans = timer.windows(blk.step, steps, seconds=0.4, at_least=3, at_most=9)
+    launches = (gpu.launch_count - launches0) // len(ms_list)
+    value = cfg.M * steps / (ms * 1e-3)
+    out = {"workload": workload_name(cfg), "parallelism": f"token-sharded x{world} at fixed M: {rows} rows per rank, no exchange",
+           "scaling": "strong", "value": value, "unit": UNIT, "ms_per_step": ms / steps, "steps": steps, "windows": len(ms_list),
+           "tops_main_product": value / cfg.M * cfg.ops / 1e12, "gpu_launches": int(launches),
+           "sm_mhz": clocks.summary(spans[0][0], spans[-1][1])["sm_mhz"]}
+    del blk
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_ours(args, cfg, rank, world):
@@ -220,194 +401,93 @@ def run_ours(args, cfg, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     gpu = Gpu(device=local)
-    if args.overlap:
-        gpu.set_launch_overlap(True)
     dev = gpu.torch_device
-    if args.parallel == "tp":
-        return run_tensor_parallel(args, cfg, rank, world, gpu)
-    blk = BlockLinears(gpu, cfg, seed=1234 + rank)
-
-    def barrier():
+    timer = Timer(gpu, world)
+    wl = workload_name(cfg)
+    with ClockSampler(local) as clocks:
+        probe = int8_peak_probe(gpu, clocks) if (rank == 0 and not args.no_probe) else None
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize(dev)
+            return run_sharded(args, cfg, rank, world, gpu, timer, clocks, probe)
 
-    def timed(fn, steps):
-        """K calls of fn between two events on the launching stream; returns milliseconds (max over ranks)."""
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        start.record(gpu.stream)
-        for _ in range(steps):
-            fn()
-        end.record(gpu.stream)
-        torch.cuda.synchronize(dev)
-        ms = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
-        barrier()
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        blk = BlockLinears(gpu, cfg, seed=1234)
+        res = time_block(gpu, blk, cfg, cfg.M, args, timer, clocks, probe["peak_tops"] if probe else None)
+        value = cfg.M / (res["ms_per_step"] * 1e-3)
+        e2e = None
+        if not args.no_e2e:
+            e2e, bufs = time_e2e(blk, timer, cfg.M, args.steps)
+            del bufs
 
-    # ---- device-resident throughput: inputs already in HBM --------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
-        blk.step()
-    with ClockSampler(local) as clocks:
-        launches0 = gpu.launch_count
-        t_load = time.time()
-        ms = timed(blk.step, args.steps)
-        launches = gpu.launch_count - launches0
-        # The timed region lasts milliseconds, shorter than one nvidia-smi sample. Keep the same steps running back
-        # to back for about a second more so that the clock record is of this load; only samples taken from the
-        # start of the timed region to the end of this window count.
-        extra_steps = 0
-        while time.time() - t_load < 1.2:
-            for _ in range(args.steps):
-                blk.step()
-            extra_steps += args.steps
-            torch.cuda.synchronize(dev)
-        clocks.t_from, clocks.t_to = t_load, time.time()
-        time.sleep(0.15)  # let the sampler's last line arrive
-    gpu.wait()
-    tokens = cfg.M * world * args.steps
-    value = tokens / (ms * 1e-3)
+        # the other producer of int8 activations, norm_mod_q8, at the block's hidden size (not part of the step)
+        hidden = blk.layers[0].wt.K
+        xres = torch.randn(blk.layers[0].m_pad, hidden, device=dev) * 3
+        modt = torch.randn(3, 2, hidden, device=dev)
+        rtt = torch.randint(0, 3, (blk.layers[0].m_pad,), device=dev, dtype=torch.uint8)
+        X32, MODT, RTT = gpu.wrap(xres), gpu.wrap(modt), gpu.wrap(rtt)
+        l0 = blk.layers[0]
+        norm_step = lambda: ops_mod.norm_mod_q8(gpu, X32, MODT, RTT, l0.a8, l0.sa, cfg.M, hidden, eps=1e-5, block=cfg.block)  # noqa: E731
+        for _ in range(3):
+            norm_step()
+        norm_ms, _, _ = timer.windows(norm_step, args.steps, seconds=0.2)
+        norm_ms /= args.steps
+        norm_bytes = cfg.M * (4 * hidden + hidden + 4)
+        hbm = hbm_peak()[0]
+        norm_extra = {"kernel": "rot_q8_tma_kernel with the norm + modulation front end", "rows": cfg.M, "channels": hidden,
+                      "us": norm_ms * 1e3, "achieved_gbs": norm_bytes / (norm_ms * 1e-3) / 1e9,
+                      "frac_of_measured_hbm": norm_bytes / (norm_ms * 1e-3) / 1e9 / hbm}
+        del blk, xres, X32
+        torch.cuda.empty_cache()
+        second = None if args.no_config4 or config_number(cfg) == 4 else token_sharded_config4(gpu, args, timer, clocks, rank, world)
+        gpu.wait()
 
-    # ---- per-kernel durations for the roofline: the step's product launches alone, then its rotate+quantise launches
-    # alone, each group K times back to back between one event pair (an event pair per launch would put the launch gaps
-    # of 15-microsecond kernels into the figure). With a LoRA term the group also holds the narrow T products.
-    peaks = measured_peaks()
-    gemm_ops = rot_bytes = 0
-    blk.step()
-    gemm_s = timed(blk.gemm_only, args.steps) * 1e-3
-    rot_s = timed(blk.rot_only, args.steps) * 1e-3
-    for l in blk.layers:
-        gemm_ops += 2 * l.m_pad * l.wt.K * l.wt.N * args.steps
-        rot_bytes += blk.M * ((4 if l.swiglu_in else 2) * l.wt.K + l.wt.K + 4) * args.steps
-    achieved_tops = gemm_ops / gemm_s / 1e12
-    rot_gbs = rot_bytes / rot_s / 1e9
-    wl = workload_name(cfg)
-    roofline = {"bound": "tensor", "kernel": "gemm_w8a8_kernel (tcgen05 kind::i8)", "achieved": achieved_tops,
-                "peak": peaks["int8_tops"], "unit": "TOP/s", "frac": achieved_tops / peaks["int8_tops"],
-                "traffic": NCU_TRAFFIC_BYTES.get(wl.split(":")[0]),
-                "algorithmic_bytes": sum(l.m_pad * l.wt.K + l.wt.N * l.wt.K + 2 * l.m_pad * l.wt.N for l in blk.layers) / len(blk.layers),
-                "peak_source": peaks["source"],
-                "frac_of_nominal_4500": achieved_tops / NOMINAL_INT8_TOPS,
-                "time_share": gemm_s / (gemm_s + rot_s)}
-    roofline_rot = {"bound": "hbm", "kernel": "rot_q8_tma_kernel (TMA-fed rotate + quantise)", "achieved": rot_gbs, "peak": peaks["hbm_gbs"],
-                    "unit": "GB/s", "frac": rot_gbs / peaks["hbm_gbs"], "traffic": None,
-                    "time_share": rot_s / (gemm_s + rot_s)}
-
-    # ---- end to end through the public API with HOST buffers: H2D of every input, D2H of every output ---------------
-    e2e = None
-    if not args.no_e2e:
-        host_in, host_out = blk.host_buffers()
-        for h, x in zip(host_in, blk.inputs):
-            if h is not None:
-                h.copy_(x.torch().cpu())
-        h2d = sum(h.numel() * 2 for h in host_in if h is not None)
-        d2h = sum(h.numel() * 2 for h in host_out if h is not None)
-
-        def e2e_step():
-            blk.step_host(host_in, host_out)
-
-        def timed_e2e(steps):
-            """Like timed(), but the region ends when the LAST download has landed in host memory."""
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            blk.sync_host()
-            barrier()
-            start.record(gpu.stream)
-            for _ in range(steps):
-                e2e_step()
-            blk._down.wait_stream(blk._up)
-            gpu.stream.wait_stream(blk._down)
-            end.record(gpu.stream)
-            blk.sync_host()
-            ms = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
-            barrier()
-            if world > 1:
-                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-            return float(ms.item())
-
-        for _ in range(2):
-            e2e_step()
-        e2e_ms = timed_e2e(args.steps)
-        e2e_value = tokens / (e2e_ms * 1e-3)
-        e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": e2e_ms / args.steps}
-
-    # ---- the other producer of int8 activations, norm_mod_q8, at the block's hidden size (not part of the step) ----
-    hidden = blk.layers[0].wt.K
-    xres = torch.randn(blk.layers[0].m_pad, hidden, device=dev) * 3
-    modt = torch.randn(3, 2, hidden, device=dev)
-    rtt = torch.randint(0, 3, (blk.layers[0].m_pad,), device=dev, dtype=torch.uint8)
-    X32, MODT, RTT = gpu.wrap(xres), gpu.wrap(modt), gpu.wrap(rtt)
-    l0 = blk.layers[0]
-
-    def norm_step():
-        ops_mod.norm_mod_q8(gpu, X32, MODT, RTT, l0.a8, l0.sa, blk.M, hidden, eps=1e-5, block=cfg.block)
-
-    for _ in range(3):
-        norm_step()
-    norm_ms = timed(norm_step, args.steps) / args.steps
-    norm_bytes = blk.M * (4 * hidden + hidden + 4)
-    norm_extra = {"kernel": "rot_q8_tma_kernel with the norm + modulation front end", "rows": blk.M, "channels": hidden, "us": norm_ms * 1e3,
-                  "achieved_gbs": norm_bytes / (norm_ms * 1e-3) / 1e9, "frac_of_measured_hbm": norm_bytes / (norm_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
-
-    if world > 1:
-        dist.barrier()
-    if rank != 0:
-        return None
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
-        "config": {"workload": wl, "block": cfg.block, "parallelism": f"token-sharded x{world} (no collective)",
-                   "l2": f"per-step working set ({sum(l.wt.N * l.wt.K for l in blk.layers) / 1e6:.0f} MB of int8 weights plus "
-                         f"{sum(2 * l.m_pad * (l.wt.K + l.wt.N) for l in blk.layers) / 1e9:.2f} GB of activations and outputs) "
-                         f"exceeds the 126 MB L2"},
-        "tops": value / cfg.M * cfg.ops / 1e12 ,
-        "roofline": roofline, "roofline_rot_q8": roofline_rot, "norm_mod_q8": norm_extra,
-        "e2e": e2e,
-        "gpu_launches": int(launches),
-        "clocks": dict(clocks.summary(), window=f"timed region + {extra_steps} identical steps run straight after it"),
+        "config": {"workload": wl, "block": cfg.block, "parallelism": "one GPU",
+                   "timing": f"{res['windows']} windows of {args.steps} steps, median window; barrier + synchronize around each",
+                   "l2": "per-step working set (weights plus activations and outputs) is several times the 126 MB L2"},
+        "tops": value / cfg.M * cfg.ops / 1e12,
+        "window_ms": res["window_ms"], "window_sm_mhz": res["window_clocks"],
+        "roofline": res["roofline"], "roofline_rot_q8": res["roofline_rot_q8"], "norm_mod_q8": norm_extra,
+        "int8_probe": probe, "e2e": e2e, "gpu_launches": res["launches_per_window"], "clocks": res["clocks"],
+        "config4_token_sharded": second,
     }
-    if world == 1 and not args.no_cpu:
-        rows = args.cpu_rows or 1024
-        cpu_value, cpu_dt = time_cpu(cfg, rows, 2, 1)
-        line["cpu_baseline"] = {
-            "value": cpu_value, "unit": UNIT, "cores": host_threads(), "kind": "port",
-            "sample": f"{rows} of {cfg.M} rows of every linear per step, 2 timed steps after 1 warm-up: the reference's NumPy "
-                      f"arithmetic (fp32 rotation matmul, absmax int8, float64 BLAS product, bias, bf16 store)"}
+    if not args.no_cpu:
+        rows = args.cpu_rows or (1024 if cfg.ops < 4e12 else 256)
+        cpu_value, _ = time_cpu(cfg, rows, 2, 1)
+        line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": host_threads(), "kind": "port",
+                                "sample": cpu_sample_text(cfg, rows) + "; 2 timed steps after 1 warm-up"}
     return line
 
 
-def run_tensor_parallel(args, cfg, rank, world, gpu):
-    """One block of cfg.M tokens over all ranks: QKV and w1|w3 column-parallel, out and w2 row-parallel with a MAX
-    all-reduce of the row maxima and a SUM all-reduce of the partial products. Strong scaling; device-resident."""
+def run_sharded(args, cfg, rank, world, gpu, timer, clocks, probe):
+    """N > 1. Configs with a LoRA term on every linear and column/row-parallel roles (config 2): every linear
+    N-sharded (column-parallel), no exchange. Otherwise ONE block over the ranks, column / row / column / row."""
     import torch
     import torch.distributed as dist
-    from h3metal_b200.parallel import TensorParallelBlock
-    if world == 1 and not dist.is_initialized():
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29531")
-        dist.init_process_group("nccl", rank=0, world_size=1, device_id=gpu.torch_device)
-    blk = TensorParallelBlock(gpu, None, cfg, seed=99, reduce=args.reduce, scatter=args.scatter)
+    from h3metal_b200 import parallel
     dev = gpu.torch_device
-    for _ in range(max(args.warmup, 3)):
-        blk.step()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    dist.barrier()
-    torch.cuda.synchronize(dev)
-    start.record(gpu.stream)
-    for _ in range(args.steps):
-        blk.step()
-    end.record(gpu.stream)
-    torch.cuda.synchronize(dev)
-    ms = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    # where the step's time goes: one event pair per layer (its rotate+quantise, product and communication), max over ranks
+
+    # ---- parity first: a timed configuration that was not checked proves nothing --------------------------------
+    verdict = parallel.check_sharded_chain(gpu, None, reduce="push")
+    flags = [None] * world
+    dist.all_gather_object(flags, verdict)
+    exact = all(f["exact"] for f in flags)
+    if not exact:
+        if rank == 0:
+            print(json.dumps({"parity": {"ranks": world, "exact": False, "failed": [f["failed"] for f in flags]}}), flush=True)
+        raise SystemExit(3)
+
+    all_column = bool(cfg.lora_rank)
+    blk = parallel.TensorParallelBlock(gpu, None, cfg, seed=99, reduce="push", all_column=all_column)
+    res = time_block(gpu, blk, cfg, cfg.M, args, timer, clocks)
+    value = cfg.M / (res["ms_per_step"] * 1e-3)
+
+    # where the step's time goes: one event pair per layer (its rotate+quantise, product and exchange), max over ranks
     n_layers = len(blk.layers)
     marks = [[torch.cuda.Event(enable_timing=True) for _ in range(n_layers + 1)] for _ in range(args.steps)]
-    dist.barrier()
-    torch.cuda.synchronize(dev)
+    timer.barrier()
     for s in range(args.steps):
         prev = None
         for i, (layer, x) in enumerate(zip(blk.layers, blk.inputs)):
@@ -415,131 +495,71 @@ def run_tensor_parallel(args, cfg, rank, world, gpu):
             prev = layer(prev if x is None else x)
         marks[s][n_layers].record(gpu.stream)
     torch.cuda.synchronize(dev)
-    per_layer = torch.tensor([sum(marks[s][i].elapsed_time(marks[s][i + 1]) for s in range(args.steps)) / args.steps
+    per_layer = torch.tensor([float(np.median([marks[s][i].elapsed_time(marks[s][i + 1]) for s in range(args.steps)]))
                               for i in range(n_layers)], device=dev, dtype=torch.float64)
     dist.all_reduce(per_layer, op=dist.ReduceOp.MAX)
+    per_layer = per_layer.tolist()
+    link = blk.link_bytes()
+    layers = {}
+    for spec, layer, t, b in zip(cfg.layers, blk.layers, per_layer, link):
+        role = "column" if isinstance(layer, parallel.ColumnParallelLinear) else "row"
+        layers[f"{spec.name} {spec.K}->{spec.N} ({role})"] = {
+            "ms": round(t, 4), "nvlink_bytes_out_per_rank": int(b),
+            "link_gbs": round(b / (t * 1e-3) / 1e9, 1) if b else 0.0,
+            "frac_of_peer_copy_770": round(b / (t * 1e-3) / 1e9 / PEER_COPY_GBS, 3) if b else 0.0}
+
+    e2e = None
+    if not args.no_e2e:
+        e2e, bufs = time_e2e(blk, timer, cfg.M, args.steps)
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, round(e2e["ms_per_step"], 4))
+        e2e["h2d_bytes_per_step"] *= world   # whole job: every rank uploads its inputs and downloads its share
+        e2e["d2h_bytes_per_step"] *= world
+        e2e["per_rank"] = "bytes are the whole job's (all ranks); ms_per_step is the slowest rank's median window"
+        del bufs
+    blk.close()
+    del blk
+    torch.cuda.empty_cache()
+
+    # the same block with NCCL's int32 all-reduce (also exact) beside the pushed reduction
+    nccl = None
+    if not all_column and not args.no_variants:
+        alt = parallel.TensorParallelBlock(gpu, None, cfg, seed=99, reduce="int32")
+        for _ in range(3):
+            alt.step()
+        ms, ms_list, _ = timer.windows(alt.step, args.steps, seconds=0.3, at_least=3, at_most=5)
+        nccl = {"reduce": "NCCL all-reduce of int32 partial accumulators (exact)", "ms_per_step": ms / args.steps,
+                "nvlink_bytes_out_per_rank_and_row_layer": alt.link_bytes()[1]}
+        alt.close()
+        del alt
+        torch.cuda.empty_cache()
+
+    second = None if args.no_config4 else token_sharded_config4(gpu, args, timer, clocks, rank, world)
     gpu.wait()
+    dist.barrier()
     if rank != 0:
         return None
-    ms = float(ms.item())
-    value = cfg.M * args.steps / (ms * 1e-3)
-    return {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": workload_name(cfg), "block": cfg.block,
-                       "parallelism": f"tp{world}: column-parallel qkv/w1w3, row-parallel out/w2 ({args.reduce} {'reduce-scatter' if args.scatter else 'all-reduce'})"},
-            "tops": value / cfg.M * cfg.ops / 1e12,
-            "layer_ms": {f"{spec.K}->{spec.N} ({spec.parallel})": round(float(t), 4)
-                         for spec, t in zip(cfg.layers, per_layer.tolist())},
-            "gpu_launches": None}
-
-
-def library_int8_probe():
-    """Yardstick, not part of the path: what the vendor library's int8 GEMM (cuBLASLt through torch._int_mm, int32
-    output, no epilogue) and its bf16 GEMM reach on this GPU under the same power cap, for cubes of three sizes.
-    Prints one JSON line."""
-    import torch
-    out = {"probe": "library int8 / bf16 GEMM", "results": []}
-    for n in (4096, 8192, 16384):
-        a = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
-        b = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8).t()
-        x = torch.randn(n, n, device="cuda", dtype=torch.bfloat16)
-        y = torch.randn(n, n, device="cuda", dtype=torch.bfloat16)
-        reps = 20 if n < 16384 else 8
-        row = {"n": n}
-        for name, fn in (("int8_tops", lambda: torch._int_mm(a, b)), ("bf16_tflops", lambda: x @ y)):
-            for _ in range(3):
-                fn()
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            start.record()
-            for _ in range(reps):
-                fn()
-            end.record()
-            torch.cuda.synchronize()
-            row[name] = 2 * n ** 3 / (start.elapsed_time(end) / reps * 1e-3) / 1e12
-        out["results"].append(row)
-    print(json.dumps(out), flush=True)
-
-
-def whole_block(args):
-    """Not the headline: one Z-Image-shaped block END TO END on one GPU (both quantising kernels with their norm
-    front end, the four int8 products, the fused residual update, and attention + q/k norm + rotary from PyTorch),
-    to show what share of a block the path is. Prints one JSON line."""
-    import torch
-    from h3metal_b200.gpu import Gpu
-    from h3metal_b200.zimage_block import ZImageBlock
-    gpu = Gpu(device=0)
-    M = 4608
-    blk = ZImageBlock(gpu, M, 3840, 30, 10240, block=128, seed=0)
-    x = gpu.wrap(torch.randn(blk.m_pad, 3840, device=gpu.torch_device))
-    pending = None
-    for _ in range(3):
-        pending = blk.forward(x, pending)
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    start.record(gpu.stream)
-    for _ in range(args.steps):
-        pending = blk.forward(x, pending)
-    end.record(gpu.stream)
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(end) / args.steps
-    gpu.profile(True)
-    blk.forward(x, pending)
-    path_s = sum(s for _, s in gpu.profile_take())
-    gpu.profile(False)
-    print(json.dumps({"workload": "one Z-Image-Turbo-shaped block, M=4608, attention by PyTorch SDPA", "ms_per_block": ms,
-                      "tokens_per_s": M / (ms * 1e-3), "path_kernels_ms": path_s * 1e3,
-                      "path_share": path_s * 1e3 / ms}), flush=True)
-
-
-def sweep(args):
-    """Not the headline: the stress sweep of config 4 on one GPU. M = 66560 rows; for K in 3072 / 6144 / 16384 the
-    rotate+quantise kernel at rotation blocks 64 / 128 / 256 (GB/s of algorithmic bytes, inputs of 0.4-2.2 GB, far
-    larger than L2) and the K -> 6144 product (TOP/s). Device timing with CUDA events after warm-up; one JSON line."""
-    import torch
-    from h3metal_b200 import ops, workloads
-    from h3metal_b200.gpu import Gpu
-    gpu = Gpu(device=0)
-    dev = gpu.torch_device
-    peaks = measured_peaks()
-    M, N = 66560, 6144
-
-    def timed(fn, n):
-        for _ in range(3):
-            fn()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize(dev)
-        start.record(gpu.stream)
-        for _ in range(n):
-            fn()
-        end.record(gpu.stream)
-        torch.cuda.synchronize(dev)
-        return start.elapsed_time(end) * 1e-3 / n
-
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(4)
-    rows = []
-    for K in (3072, 6144, 16384):
-        x = gpu.wrap(workloads.activations_torch(gen, M, K, round(0.002 * K), dev))
-        a8, sa = gpu.empty((M, K), "i8"), gpu.empty((M,), "f32")
-        for block in (64, 128, 256):
-            t = timed(lambda: ops.rot_q8(gpu, x, a8, sa, M, K, block=block), 10)
-            gbs = M * (3 * K + 4) / t / 1e9
-            rows.append({"kernel": "rot_q8", "K": K, "block": block, "us": t * 1e6, "GB/s": gbs,
-                         "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]})
-        codes, scales = workloads.weight_torch(gen, N, K, dev)
-        wt = ops.QWeight("q8", gpu.wrap(codes), gpu.wrap(scales), N, K)
-        out = gpu.empty((M, N), "bf16")
-        t = timed(lambda: ops.gemm(gpu, a8, wt, out, M, sa=sa, tile=(128, 32, 4)), 5)
-        tops = 2.0 * M * N * K / t / 1e12
-        rows.append({"kernel": "gemm_w8a8", "K": K, "N": N, "us": t * 1e6, "TOP/s": tops,
-                     "frac_of_measured_int8": tops / peaks["int8_tops"], "frac_of_nominal_4500": tops / NOMINAL_INT8_TOPS})
-        del x, a8, out, wt, codes
-        torch.cuda.empty_cache()
-    gpu.wait()
-    print(json.dumps({"workload": f"config 4 sweep: M={M}, K in 3072/6144/16384, N={N}, rotation blocks 64/128/256",
-                      "peak_source": peaks["source"], "rows": rows}), flush=True)
+    if all_column:
+        how = f"every linear N-sharded (column-parallel) x{world}, LoRA rows follow the weight's; no exchange"
+    else:
+        how = (f"tp{world}: ONE block of M tokens; qkv and w1|w3 column-parallel, out and w2 row-parallel with the exact int32 "
+               f"reduction pushed over NVLink by the product kernel (reduce-scatter by peer stores, owner's sum + epilogue, "
+               f"all-gather by peer stores); whole-row scales by a pushed MAX exchange")
+    return {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": workload_name(cfg), "block": cfg.block, "parallelism": how,
+                   "timing": f"{res['windows']} windows of {args.steps} steps, median window of the per-window maximum over ranks",
+                   "l2": "per-step working set per rank exceeds the 126 MB L2"},
+        "tops": value / cfg.M * cfg.ops / 1e12,
+        "parity": {"ranks": world, "exact": True,
+                   "what": "column-parallel -> swiglu quantiser -> row-parallel (push) chain equals each rank's own one-GPU result bit for bit"},
+        "window_ms": res["window_ms"], "window_sm_mhz": res["window_clocks"],
+        "layers": layers, "nccl_int32_allreduce": nccl, "int8_probe": probe,
+        "e2e": e2e, "gpu_launches": res["launches_per_window"], "clocks": res["clocks"],
+        "config4_token_sharded": second,
+    }
 
 
 def main():
@@ -548,37 +568,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=1)
+    ap.add_argument("--config", type=int, default=3)
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (0 = default)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (it pins GBs of host memory on the largest configs)")
-    ap.add_argument("--parallel", default="token", choices=["token", "tp"],
-                    help="N > 1: token = every rank its own M tokens (default, weak scaling); tp = ONE block of M tokens "
-                         "sharded column-/row-parallel over the ranks with NCCL all-reduces (strong scaling)")
-    ap.add_argument("--reduce", default="int32", choices=["int32", "f32", "bf16", "push", "push_bf16"],
-                    help="tp: what the row-parallel layers reduce (int32 = bit-exact, NCCL; push = bit-exact, partial "
-                         "accumulators stored by the product kernel straight into the row owners' memory over NVLink; "
-                         "push_bf16 = the same with bf16 partials)")
-    ap.add_argument("--scatter", action="store_true",
-                    help="tp: reduce-scatter instead of all-reduce (every rank finishes its M / N_gpus rows)")
-    ap.add_argument("--overlap", action="store_true",
-                    help="launch the kernels with programmatic dependent launch (off by default: slower on this block)")
-    ap.add_argument("--library-int8-probe", action="store_true",
-                    help="time the vendor library's int8 and bf16 GEMMs on this GPU (a yardstick; runs nothing of the path)")
-    ap.add_argument("--sweep", action="store_true",
-                    help="the K x rotation-block stress sweep of config 4 (M = 66560) instead of the block step")
-    ap.add_argument("--whole-block", action="store_true",
-                    help="time one whole Z-Image-shaped block with PyTorch attention (context for the path's share)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (it pins GBs of host memory)")
+    ap.add_argument("--no-probe", action="store_true", help="skip the int8 issue-rate probe")
+    ap.add_argument("--no-config4", action="store_true", help="skip the token-sharded second object (config 4)")
+    ap.add_argument("--no-variants", action="store_true", help="N > 1: skip the NCCL all-reduce run beside the pushed one")
     args = ap.parse_args()
-    if args.library_int8_probe:
-        library_int8_probe()
-        return
-    if args.whole_block:
-        whole_block(args)
-        return
-    if args.sweep:
-        sweep(args)
-        return
 
     from h3metal_b200 import workloads
     cfg = workloads.CONFIGS[args.config]

@@ -16,7 +16,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libh3b200.so")
-SOURCES = ("capi.cu", "rot_q8.cu", "rot_q8_tma.cu", "norm_mod_q8.cu", "gemm_w8a8.cu", "gemm_w8a8_pair.cu", "dequant.cu", "peer.cu")
+SOURCES = ("capi.cu", "rot_q8.cu", "rot_q8_tma.cu", "norm_mod_q8.cu", "gemm_w8a8.cu", "gemm_w8a8_pair.cu", "dequant.cu", "peer.cu", "mma_probe.cu")
 HEADERS = ("kernels.h", "ptx.cuh", "rot_common.cuh", "gemm_common.cuh", os.path.join("..", "..", "include", "h3b200.h"))
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # -fmad=false: the rotate+quantise arithmetic and the dequantising epilogue are defined operation by operation;
@@ -40,7 +40,7 @@ def _stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles the three translation units and links the shared library; returns its path."""
+    """Compiles the translation units and links the shared library; returns its path."""
     if not force and not _stale():
         return LIB
     nvcc = _nvcc()

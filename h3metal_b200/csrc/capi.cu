@@ -183,6 +183,40 @@ struct h3b_ctx {
   }
 };
 
+// ---- scratch of the product with a LoRA term for callers that cannot allocate (h3b_gemm_w8a8_lora_noalloc) ----------
+// Its T scratch lives in the library image instead of in caller memory: a file-scope device array. In host code the
+// array's NAME is only a stand-in for the symbol, not a device address, so the address is fetched once per device
+// with cudaGetSymbolAddress (below) and that pointer is what the kernels and the TMA descriptor receive.
+static __device__ __align__(256) unsigned short g_lora_t_static[H3B_NOALLOC_MAX_T_VALUES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void *g_static_addr[kMaxDevices] = {};
+
+// Device address of g_lora_t_static on `device`, which the caller has made current. Looked up once per device and
+// remembered. h3b_open() calls this at set-up: the look-up makes the runtime load this file's device code, and with it
+// place the array in that device's memory, while the context is allocating anyway - not in the middle of a caller's
+// first no-alloc product.
+void *static_scratch(int device) {
+  if (device < 0 || device >= kMaxDevices) {
+    fail("no-alloc product: device index out of range");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_addr[device]) {
+    void *ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_lora_t_static);
+    if (e != cudaSuccess || !ptr) {
+      fail_cuda("cudaGetSymbolAddress(static LoRA scratch)", e == cudaSuccess ? cudaErrorUnknown : e);
+      return nullptr;
+    }
+    g_static_addr[device] = ptr;
+  }
+  return g_static_addr[device];
+}
+}  // namespace
+
 extern "C" {
 
 const char *h3b_last_error(void) { return g_error.c_str(); }
@@ -236,6 +270,11 @@ h3b_ctx *h3b_open(int device) {
   ctx->pair_stages = h3b::gemm_pair_pick_stages(ctx->prop.sharedMemPerBlockOptin);
   ctx->pair_clusters = ctx->pair_stages >= 2 ? h3b::gemm_pair_max_clusters(ctx->pair_stages) : 0;
   cudaGetLastError();  // an occupancy query that failed must not poison the next launch check
+  // the static scratch of h3b_gemm_w8a8_lora_noalloc is resolved (and thereby placed on this device) now, at set-up
+  if (device < kMaxDevices && !static_scratch(device)) {
+    delete ctx;
+    return nullptr;
+  }
   return ctx;
 }
 
@@ -439,13 +478,15 @@ int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int /*lora*/) {
 }
 
 // Checks the arguments of one product and enqueues it. cached_maps: TMA descriptors come from (and go into) the
-// context's cache; false builds them on the stack so that the call allocates nothing, host memory included.
+// context's cache; false builds them on the stack: no device allocation, and no host allocation either outside
+// profile mode (which records a time per launch) and error messages. check_only: every check, no launch.
 static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
                         const float *sw, const float *sa, const float *bias, void *C, int c_dtype, int64_t c_stride,
                         int M, int N, int K, const void *lora_T, int64_t t_stride, const void *lora_B,
                         int64_t b_stride, int R, const int32_t *lora_ranges, bool cached_maps,
                         const uint8_t *rtype = nullptr, const float *gate = nullptr, int64_t g_stride = 0,
-                        void *const *push_slots = nullptr, int push_world = 0, int push_rows = 0) {
+                        void *const *push_slots = nullptr, int push_world = 0, int push_rows = 0,
+                        bool check_only = false) {
   if (!ctx) return fail("null context");
   const bool push = push_slots != nullptr;
   if (push) {
@@ -532,6 +573,7 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
   const long long tiles = static_cast<long long>(m_tiles) * n_tiles;
   g.status = ctx->status_dev;
   g.overlap = (ctx->overlap != 0 && !ctx->profile) ? 1 : 0;
+  if (check_only) return 0;
 
   cudaEvent_t ps = nullptr;
   if (ctx->before_launch(&ps)) return -1;
@@ -666,6 +708,7 @@ static int reduce_enqueue(h3b_ctx *ctx, const void *stage, int64_t slot_stride, 
   r.stage = stage; r.slot_stride = slot_stride; r.stage_stride = stage_stride; r.stage_dtype = stage_dtype; r.world = world;
   r.sa = sa; r.sw = sw; r.bias = bias; r.n_out = n_out; r.c_stride = c_stride; r.c_dtype = c_dtype; r.rows = rows; r.N = N;
   r.row0 = row0;
+  r.status = ctx->status_dev;
   if (gate) {
     if (!rtype) return fail("reduce_dequant (gated): null row types");
     if (g_stride < N || (g_stride * 4) % 16 || reinterpret_cast<uintptr_t>(gate) % 16) return fail("reduce_dequant (gated): gate rows must be 16-byte aligned and at least N long");
@@ -696,38 +739,6 @@ int h3b_reduce_dequant_gated(h3b_ctx *ctx, const void *stage, int64_t slot_strid
                         rows, N, row0, rtype, gate, g_stride);
 }
 
-// ---- the product with a LoRA term for callers that cannot allocate ------------------------------------------------
-// Its T scratch lives in the library image instead of in caller memory: a file-scope device array. In host code the
-// array's NAME is only a stand-in for the symbol, not a device address, so the address is fetched once per device
-// with cudaGetSymbolAddress (below) and that pointer is what the kernels and the TMA descriptor receive.
-static __device__ __align__(256) unsigned short g_lora_t_static[H3B_NOALLOC_MAX_T_VALUES];
-
-namespace {
-constexpr int kMaxDevices = 64;
-std::mutex g_static_mu;
-void *g_static_addr[kMaxDevices] = {};
-
-// Device address of g_lora_t_static on the context's device (which the caller has made current). Looked up on the
-// first call per device and remembered.
-void *static_scratch(h3b_ctx *ctx) {
-  if (ctx->device < 0 || ctx->device >= kMaxDevices) {
-    fail("no-alloc product: device index out of range");
-    return nullptr;
-  }
-  std::lock_guard<std::mutex> lock(g_static_mu);
-  if (!g_static_addr[ctx->device]) {
-    void *ptr = nullptr;
-    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_lora_t_static);
-    if (e != cudaSuccess || !ptr) {
-      fail_cuda("cudaGetSymbolAddress(static LoRA scratch)", e == cudaSuccess ? cudaErrorUnknown : e);
-      return nullptr;
-    }
-    g_static_addr[ctx->device] = ptr;
-  }
-  return g_static_addr[ctx->device];
-}
-}  // namespace
-
 int h3b_gemm_w8a8_lora_noalloc(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const int8_t *W, int64_t w_stride,
                                const float *sw, const float *sa, const float *bias, void *C, int c_dtype,
                                int64_t c_stride, int M, int N, int K, const int8_t *lora_A, int64_t la_stride,
@@ -743,8 +754,14 @@ int h3b_gemm_w8a8_lora_noalloc(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, 
                 std::to_string(static_cast<unsigned long long>(H3B_NOALLOC_MAX_T_VALUES)) +
                 " (8 MiB); split the rows or use h3b_gemm_w8a8 with your own T buffer");
   if (ctx->make_current()) return -1;
-  void *T = static_scratch(ctx);
+  void *T = static_scratch(ctx->device);
   if (!T) return -1;
+  // both products' arguments are checked before the first launch: a refused call leaves the shared array untouched
+  if (gemm_enqueue(ctx, A, a_stride, lora_A, la_stride, lora_sw, sa, nullptr, T, H3B_F16, R, M, R, K, nullptr, 0, nullptr,
+                   0, 0, nullptr, false, nullptr, nullptr, 0, nullptr, 0, 0, true) ||
+      gemm_enqueue(ctx, A, a_stride, W, w_stride, sw, sa, bias, C, c_dtype, c_stride, M, N, K, T, R, lora_B, b_stride, R,
+                   lora_ranges, false, nullptr, nullptr, 0, nullptr, 0, 0, true))
+    return -1;
   // T[m][j] = fp16(acc * sa[m] * lora_sw[j]) for every one of the M rows and R columns: the whole region the main
   // product reads is overwritten, so nothing of an earlier call survives into this one and nothing needs clearing.
   if (gemm_enqueue(ctx, A, a_stride, lora_A, la_stride, lora_sw, sa, nullptr, T, H3B_F16, R, M, R, K, nullptr, 0, nullptr,
@@ -760,6 +777,45 @@ int h3b_selftest_expire_wait(h3b_ctx *ctx) {
   if (ctx->before_launch(&ps)) return -1;
   // about a millisecond at the part's clocks: long enough to be a real wait, short enough for a test
   return ctx->after_launch("self-test launch", h3b::launch_expire_wait(ctx->status_dev, 2000000LL, ctx->stream));
+}
+
+int h3b_mma_rate_probe(h3b_ctx *ctx, int pair, int iters, double out[5]) {
+  if (!ctx || !out) return fail("mma_rate_probe: null argument");
+  if (iters < 1 || iters > 4000000) return fail("mma_rate_probe: iters must be in [1, 4000000]");
+  if (ctx->make_current()) return -1;
+  int ctas = ctx->prop.multiProcessorCount;
+  unsigned long long *cycles = nullptr;
+  cudaError_t e = cudaMalloc(&cycles, sizeof(unsigned long long) * ctas);
+  if (e != cudaSuccess) return fail_cuda("mma_rate_probe: cudaMalloc", e);
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  std::vector<unsigned long long> host(ctas, 0ull);
+  float ms = 0;
+  int rc = 0;
+  if ((e = cudaEventCreate(&t0)) != cudaSuccess || (e = cudaEventCreate(&t1)) != cudaSuccess ||
+      (e = cudaMemsetAsync(cycles, 0, sizeof(unsigned long long) * ctas, ctx->stream)) != cudaSuccess ||
+      (e = cudaEventRecord(t0, ctx->stream)) != cudaSuccess ||
+      (e = h3b::launch_mma_probe(pair != 0, iters, &ctas, ctx->status_dev, cycles, ctx->stream)) != cudaSuccess ||
+      (e = cudaEventRecord(t1, ctx->stream)) != cudaSuccess || (e = cudaStreamSynchronize(ctx->stream)) != cudaSuccess ||
+      (e = cudaEventElapsedTime(&ms, t0, t1)) != cudaSuccess ||
+      (e = cudaMemcpy(host.data(), cycles, sizeof(unsigned long long) * ctas, cudaMemcpyDeviceToHost)) != cudaSuccess)
+    rc = fail_cuda("mma_rate_probe", e);
+  if (t0) cudaEventDestroy(t0);
+  if (t1) cudaEventDestroy(t1);
+  cudaFree(cycles);
+  if (rc) return rc;
+  ++ctx->launches;
+  unsigned long long worst = 0;
+  for (int i = 0; i < ctas; ++i) {
+    if (host[i] == 0) return fail("mma_rate_probe: a CTA's wait for its last instruction ran out");
+    if (host[i] > worst) worst = host[i];
+  }
+  const double ops_per_cta = 2.0 * 128 * 256 * 32 * 4.0 * iters;  // each SM multiplies 128 x 256 x 32 per instruction
+  out[0] = ms * 1e-3;
+  out[1] = static_cast<double>(worst);
+  out[2] = ops_per_cta / static_cast<double>(worst);
+  out[3] = ops_per_cta * ctas / (ms * 1e-3) / 1e12;
+  out[4] = ctas;
+  return 0;
 }
 
 void h3b_commit(h3b_ctx *) {}

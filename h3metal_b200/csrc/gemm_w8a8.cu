@@ -154,6 +154,9 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
       constexpr uint32_t idesc_f16 = umma_instr_desc(1, 0, kBM, BN);  // f32 accumulate, f16 x f16
       uint32_t it = 0, at = 0;
       bool ok = true;
+      // operand descriptors of stage 0; stage s adds s * kStage bytes (in 16-byte units) to the address field
+      const uint64_t ad0 = umma_smem_desc(base, 1024, 2);
+      const uint64_t bd0 = umma_smem_desc(base + kABytes, 1024, 2);
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++at) {
         const int as = at % ACC_STAGES;
         const uint32_t aph = (at / ACC_STAGES) & 1u;
@@ -194,9 +197,8 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
           ok = mbar_wait(full_bar(s), ph, cta_abort, g.status, kStatusMmaTimeout);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t a_addr = base + s * kStage;
-          const uint64_t ad = umma_smem_desc(a_addr, 1024, 2);
-          const uint64_t bd = umma_smem_desc(a_addr + kABytes, 1024, 2);
+          const uint64_t ad = ad0 + static_cast<uint64_t>(s) * (kStage >> 4);
+          const uint64_t bd = bd0 + static_cast<uint64_t>(s) * (kStage >> 4);
 #pragma unroll
           for (int k = 0; k < kBKBytes / 32; ++k) {  // 32 int8 of K per instruction = 32 bytes = 2 descriptor units
             umma_i8(d_acc, ad + 2u * k, bd + 2u * k, idesc_i8, (kb | k) != 0 ? 1u : 0u);

@@ -78,6 +78,10 @@ struct ReduceLaunch {
   const unsigned char *rtype;
   const float *gate;
   long long g_stride;
+  // The context's device status word (or null). A kernel earlier in the stream that gave up a bounded wait - the
+  // rendezvous before this reduction, above all - leaves a code there; the reduction then stores nothing, so that
+  // sums over staging memory a late GPU has not filled never reach anybody's output.
+  const int *status;
 };
 cudaError_t launch_reduce_dequant(const ReduceLaunch &r, int sms, cudaStream_t stream);
 
@@ -93,6 +97,11 @@ struct PeerSync {
   long long limit_cycles;
 };
 cudaError_t launch_peer_sync(const PeerSync &p, cudaStream_t stream);
+
+// Issue-rate probe of the int8 tensor pipe (mma_probe.cu). *ctas: CTAs wanted in, CTAs launched out (CTA pairs are
+// limited to what can be resident at once). cycles[cta] receives each CTA's clock64 span, 0 if its wait ran out.
+cudaError_t launch_mma_probe(int pair, int iters, int *ctas, int *status, unsigned long long *cycles,
+                             cudaStream_t stream);
 
 // Self-test: a kernel whose bounded wait must expire after `limit_cycles` and report through the status word.
 cudaError_t launch_expire_wait(int *status, long long limit_cycles, cudaStream_t stream);

@@ -14,6 +14,8 @@
 //                           the product's epilogue in the reference's operation order (kernels/gemm.metal:238-255
 //                           of the reference) and store the rows, optionally into every GPU's output (all-gather by
 //                           peer stores). HBM-bound: world x 4 (or 2) bytes read per element, 2 written per copy.
+//                           If a kernel before it in the stream gave up a bounded wait (the rendezvous, above all),
+//                           it stores nothing: partial sums never reach an output.
 //
 // The reference is single-GPU; nothing here has a counterpart in it.
 #include <cuda_bf16.h>
@@ -81,6 +83,7 @@ __device__ __forceinline__ void store8(OUT_T *dst, const float (&v)[8]) {
 // One thread per group of 8 consecutive columns. STAGE_I32: slots hold int32 partial accumulators, else bf16 partials.
 template <typename OUT_T, bool STAGE_I32>
 __global__ void __launch_bounds__(256) reduce_dequant_kernel(const __grid_constant__ ReduceLaunch r) {
+  if (r.status != nullptr && *reinterpret_cast<const volatile int *>(r.status) != kStatusOk) return;
   const long long groups_per_row = r.N / 8;
   const long long total = static_cast<long long>(r.rows) * groups_per_row;
   const bool has_bias = r.bias != nullptr;

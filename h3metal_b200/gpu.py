@@ -88,6 +88,7 @@ def _signatures():
         "h3b_gemm_set_policy": (i32, [vp, i32, i32, i32]),
         "h3b_rot_set_policy": (i32, [vp, i32, i32, i32]),
         "h3b_selftest_expire_wait": (i32, [vp]),
+        "h3b_mma_rate_probe": (i32, [vp, i32, i32, ctypes.POINTER(dbl)]),
         "h3b_commit": (None, [vp]),
         "h3b_wait": (dbl, [vp]),
         "h3b_set_profile": (None, [vp, i32]),
@@ -534,6 +535,14 @@ class Gpu:
         n = lib().h3b_profile_take(self.ctx, out, 100000)
         names, self.names = self.names[:n], self.names[n:]
         return list(zip(names, out[:n]))
+
+    def mma_rate_probe(self, pair: bool = False, iters: int = 40000) -> dict:
+        """Issue rate of the int8 tensor pipe from operands resident in shared memory (no TMA, no epilogue): the
+        measured ceiling of the product, as the reference measures its matrix units (bench/hw/mma_rate.py:9-24).
+        Blocking; one launch of about iters x 0.3 microseconds."""
+        out = (ctypes.c_double * 5)()
+        self._check(lib().h3b_mma_rate_probe(self.ctx, int(pair), int(iters), out))
+        return {"seconds": out[0], "cycles": out[1], "ops_per_clk_per_sm": out[2], "tops": out[3], "ctas": int(out[4])}
 
     @property
     def launch_count(self) -> int:

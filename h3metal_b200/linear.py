@@ -44,7 +44,80 @@ def upload_weight(gpu: Gpu, codes, scales, bias=None, low=None) -> ops.QWeight:
     return ops.QWeight("q8", put(codes), put(scales), int(N), int(K), bias=put(bias), low=low)
 
 
-class BlockLinears:
+class HostStaged:
+    """The step of a chain of layers for a caller whose activations live in HOST memory. The class that mixes this in
+    provides `gpu`, `layers` (callables: layer(src) -> output Tensor) and `inputs` (per layer its own device input,
+    or None when it consumes the previous layer's output)."""
+
+    def _result(self, i: int):
+        """torch view of what layer i hands back to the host."""
+        return self.layers[i].out.torch()
+
+    def host_buffers(self):
+        """Pinned host tensors for step_host(): one input per layer that reads its own input, one output per layer
+        whose result leaves the block (a layer that only feeds the next linear on the device has none)."""
+        import torch
+        ins, outs = [], []
+        for i, x in enumerate(self.inputs):
+            ins.append(None if x is None else torch.empty(x.shape, dtype=torch.bfloat16).pin_memory())
+            feeds_next = i + 1 < len(self.layers) and self.inputs[i + 1] is None
+            outs.append(None if feeds_next else torch.empty(self._result(i).shape, dtype=torch.bfloat16).pin_memory())
+        return ins, outs
+
+    def step_host(self, host_in, host_out):
+        """One pass with host inputs and outputs. Uploads run on one copy stream, kernels on the context's stream,
+        downloads on a second copy stream, chained per layer by events: the upload of layer i+1 and the download of
+        layer i-1 overlap the kernels of layer i, and (PCIe being full duplex) each other. Buffers are guarded per
+        layer, so consecutive calls overlap too. Results are in host_out after `sync_host()`."""
+        import torch
+        if not hasattr(self, "_up"):
+            dev = self.gpu.torch_device
+            self._up, self._down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+            n = len(self.layers)
+            self._in_ready = [torch.cuda.Event() for _ in range(n)]
+            self._in_free = [torch.cuda.Event() for _ in range(n)]
+            self._out_ready = [torch.cuda.Event() for _ in range(n)]
+            self._out_free = [torch.cuda.Event() for _ in range(n)]
+            self._primed = False
+        compute = self.gpu.stream
+        prev = None
+        for i, (layer, x) in enumerate(zip(self.layers, self.inputs)):
+            if x is not None:
+                if self._primed:
+                    self._up.wait_event(self._in_free[i])     # the previous call's kernels have read this input
+                with torch.cuda.stream(self._up):
+                    x.torch().copy_(host_in[i], non_blocking=True)
+                    self._in_ready[i].record(self._up)
+                compute.wait_event(self._in_ready[i])
+            if self._primed and host_out[i] is not None:
+                compute.wait_event(self._out_free[i])         # the previous call's download of this output is done
+            prev = layer(prev if x is None else x)
+            if x is not None:
+                self._in_free[i].record(compute)
+            if host_out[i] is not None:
+                self._out_ready[i].record(compute)
+                self._down.wait_event(self._out_ready[i])
+                with torch.cuda.stream(self._down):
+                    host_out[i].copy_(self._result(i), non_blocking=True)
+                    self._out_free[i].record(self._down)
+        self._primed = True
+
+    def finish_host(self):
+        """Makes the context's stream wait for every copy step_host() has issued (so that an event recorded on it
+        afterwards marks the moment the last download landed)."""
+        if hasattr(self, "_down"):
+            self._down.wait_stream(self._up)
+            self.gpu.stream.wait_stream(self._down)
+
+    def sync_host(self):
+        """Blocks until every upload, kernel and download issued by step_host() has finished."""
+        if hasattr(self, "_down"):
+            self._down.synchronize()
+            self._up.synchronize()
+        self.gpu.stream.synchronize()
+
+
+class BlockLinears(HostStaged):
     """The linears of one transformer block of `cfg` on one GPU, with synthetic weights drawn on the device.
 
     Layers whose input is the previous layer's output (swiglu_in) consume it; the others read their own input
@@ -94,66 +167,6 @@ class BlockLinears:
         """Only the product launches of a step (on the codes the last rotate+quantise left in each layer's buffers)."""
         for layer in self.layers:
             ops.gemm(self.gpu, layer.a8, layer.wt, layer.out, layer.M, sa=layer.sa, tile=(128, 32, 4))
-
-    # -- the same step for a caller whose activations live in host memory ------------------------------------------------
-    def host_buffers(self):
-        """Pinned host tensors for step_host(): one input per layer that reads its own input, one output per layer
-        whose result leaves the block (a layer that only feeds the next linear on the device has none)."""
-        import torch
-        ins, outs = [], []
-        for i, (layer, x) in enumerate(zip(self.layers, self.inputs)):
-            ins.append(None if x is None else torch.empty(x.shape, dtype=torch.bfloat16).pin_memory())
-            feeds_next = i + 1 < len(self.layers) and self.inputs[i + 1] is None
-            outs.append(None if feeds_next else torch.empty(layer.out.shape, dtype=torch.bfloat16).pin_memory())
-        return ins, outs
-
-    def step_host(self, host_in, host_out):
-        """One pass with host inputs and outputs. Uploads run on one copy stream, kernels on the context's stream,
-        downloads on a second copy stream, chained per layer by events: the upload of layer i+1 and the download of
-        layer i-1 overlap the kernels of layer i, and (PCIe being full duplex) each other. Buffers are guarded per
-        layer, so consecutive calls overlap too. Results are in host_out after `sync_host()`."""
-        import torch
-        if not hasattr(self, "_up"):
-            dev = self.gpu.torch_device
-            self._up, self._down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-            n = len(self.layers)
-            self._in_ready = [torch.cuda.Event() for _ in range(n)]
-            self._in_free = [torch.cuda.Event() for _ in range(n)]
-            self._out_ready = [torch.cuda.Event() for _ in range(n)]
-            self._out_free = [torch.cuda.Event() for _ in range(n)]
-            self._primed = False
-        compute = self.gpu.stream
-        prev = None
-        for i, (layer, x) in enumerate(zip(self.layers, self.inputs)):
-            if x is not None:
-                if self._primed:
-                    self._up.wait_event(self._in_free[i])     # the previous call's kernels have read this input
-                with torch.cuda.stream(self._up):
-                    x.torch().copy_(host_in[i], non_blocking=True)
-                    self._in_ready[i].record(self._up)
-                compute.wait_event(self._in_ready[i])
-            if self._primed and host_out[i] is not None:
-                compute.wait_event(self._out_free[i])         # the previous call's download of this output is done
-            src = prev if x is None else x
-            ops.rot_q8(self.gpu, src, layer.a8, layer.sa, layer.M, layer.wt.K, swiglu=layer.swiglu_in, block=layer.block)
-            if x is not None:
-                self._in_free[i].record(compute)
-            ops.gemm(self.gpu, layer.a8, layer.wt, layer.out, layer.M, sa=layer.sa, tile=(128, 32, 4))
-            prev = layer.out
-            if host_out[i] is not None:
-                self._out_ready[i].record(compute)
-                self._down.wait_event(self._out_ready[i])
-                with torch.cuda.stream(self._down):
-                    host_out[i].copy_(layer.out.torch(), non_blocking=True)
-                    self._out_free[i].record(self._down)
-        self._primed = True
-
-    def sync_host(self):
-        """Blocks until every upload, kernel and download issued by step_host() has finished."""
-        if hasattr(self, "_down"):
-            self._down.synchronize()
-            self._up.synchronize()
-        self.gpu.stream.synchronize()
 
     @property
     def launches_per_step(self) -> int:

@@ -27,6 +27,10 @@ row-parallel    W's columns (K) are split; the input arrives already sharded on 
                 int32 partials cross NVLink once (reduce-scatter) and the all-gather moves 2-byte outputs, a quarter
                 less traffic than an int32 all-reduce; `push_bf16` halves the first leg again.
                 K / p must be a multiple of the rotation block. A LoRA term on a row-parallel layer is not supported.
+                Failure behaviour of the push variants: the device-side rendezvous polls for about a second; when a
+                rank is late or absent the waiting rank's kernel records the give-up and returns, the reduction
+                queued behind it stores nothing (no sum over staging that was never filled reaches an output), and
+                `gpu.wait()` raises on that rank. `RowParallelLinear.recover()` on every rank re-aligns the layer.
 
 Collectives run on torch's current stream, which is also the stream the kernels are launched on, so a layer is
 one ordered sequence of kernels and collectives without host synchronisation.
@@ -38,6 +42,7 @@ import numpy as np
 
 from . import ops
 from .gpu import Gpu, Tensor
+from .linear import HostStaged
 
 
 def _dist():
@@ -129,6 +134,16 @@ class PeerBlock:
         self.epoch += 1
         self.gpu.peer_sync_native(self.base, self.rank, self.world, self.epoch, mode)
 
+    def resync(self):
+        """Host-side recovery after a rendezvous ran out on some rank (the error surfaced at that rank's wait()):
+        every rank of the group calls this; they agree on the largest epoch any of them reached, so that the next
+        rendezvous waits for a value nobody has signalled yet. Collective over the process group, no kernel."""
+        if self.world > 1:
+            dist = _dist()
+            seen = [None] * self.world
+            dist.all_gather_object(seen, self.epoch, group=self.group)
+            self.epoch = max(seen)
+
     def close(self):
         if self.base is None:
             return
@@ -166,20 +181,30 @@ class ColumnParallelLinear:
     """This rank's N / p outputs of the layer; x is the full (replicated) activation."""
 
     def __init__(self, gpu: Gpu, group, codes, scales, bias, M: int, *, block: int = 128, splits=None,
-                 swiglu_in: bool = False, out_dtype: str = "bf16", lora=None, scratch: ops.Scratch | None = None):
+                 swiglu_in: bool = False, out_dtype: str = "bf16", lora=None, scratch: ops.Scratch | None = None,
+                 n_total: int | None = None):
+        """codes int8 [N][K], scales and bias fp32 [N] of the WHOLE layer, of which this rank keeps its rows - or,
+        with n_total given, already only this rank's rows of a layer of n_total outputs (a caller that draws or
+        loads per rank need not materialise the whole weight). lora = (A [r][K], B [N][r]) is always the whole term."""
         dist = _dist()
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         N, K = codes.shape
-        self.slices = column_slices(int(N), splits, self.rank, self.world)
+        self.slices = column_slices(int(n_total or N), splits, self.rank, self.world)
+        if n_total is not None:
+            if sum(b - a for a, b in self.slices) != int(N):
+                raise ValueError(f"{N} local rows are not this rank's share of {n_total}")
+            local = [(0, int(N))]
+        else:
+            local = self.slices
         low = None
         if lora is not None:
             # (A [r][K] in the rotated input space, B [N][r]): the term is prepared from the whole B, so that its
             # normalisation and A's codes are the unsharded layer's, and this rank keeps the rows of B' it owns
             A_l, B_l = lora
             low = ops.low_rank(gpu, A_l, B_l, scratch or ops.Scratch(gpu), rows=self.slices)
-        self.wt = ops.QWeight("q8", _put(gpu, take_rows(codes, self.slices)), _put(gpu, take_rows(scales, self.slices)),
-                              sum(b - a for a, b in self.slices), int(K),
-                              bias=_put(gpu, take_rows(bias, self.slices)) if bias is not None else None, low=low)
+        self.wt = ops.QWeight("q8", _put(gpu, take_rows(codes, local)), _put(gpu, take_rows(scales, local)),
+                              sum(b - a for a, b in local), int(K),
+                              bias=_put(gpu, take_rows(bias, local)) if bias is not None else None, low=low)
         self.gpu, self.M, self.block, self.swiglu_in = gpu, M, block, swiglu_in
         self.m_pad = ops.pad_rows(M)
         self.a8 = gpu.empty((self.m_pad, int(K)), "i8")
@@ -330,41 +355,61 @@ class RowParallelLinear:
             mem.sync()  # every rank's finished rows have landed in my output
         return self.out
 
+    def recover(self):
+        """After a rendezvous of a push variant ran out (a rank was late or absent; `gpu.wait()` raised on the ranks
+        that waited in vain, and their owner-side reductions stored nothing): brings the ranks' rendezvous counters
+        and staging-buffer turns back in step. Every rank of the group calls it, between steps, with no kernel of
+        the layer in flight. The next call then runs normally."""
+        if self.push:
+            self.block_mem.resync()
+            if self.world > 1:
+                dist = _dist()
+                seen = [None] * self.world
+                dist.all_gather_object(seen, self.calls, group=self.group)
+                self.calls = max(seen)
+
     def close(self):
         if self.push:
             self.block_mem.close()
 
 
-class TensorParallelBlock:
+class TensorParallelBlock(HostStaged):
     """The four linears of a DiT block (QKV, attention-out, w1|w3, w2) sharded as column / row / column / row, with
     synthetic weights drawn per rank on the device (timing only). Inputs that the model's attention and norm kernels
-    would produce (outside this path) are synthetic buffers of the right, sharded shapes."""
+    would produce (outside this path) are synthetic buffers of the right, sharded shapes. With `all_column` every
+    linear is column-parallel (N-sharded) and reads its own full-width input: no exchange at all."""
 
-    def __init__(self, gpu: Gpu, group, cfg, seed: int = 0, reduce: str = "int32", scatter: bool = False):
+    def __init__(self, gpu: Gpu, group, cfg, seed: int = 0, reduce: str = "int32", scatter: bool = False,
+                 all_column: bool = False):
         import torch
         from . import workloads
         dist = _dist()
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         gen = torch.Generator(device=gpu.torch_device)
         gen.manual_seed(seed * 1000 + rank)
+        rng = np.random.default_rng(seed)  # the same on every rank: low-rank terms are prepared from the whole B
         dev = gpu.torch_device
         M, m_pad = cfg.M, ops.pad_rows(cfg.M)
         self.gpu, self.cfg, self.layers, self.inputs = gpu, cfg, [], []
+        self.rank, self.world = rank, world
+        self.scratch = ops.Scratch(gpu)
         for spec in cfg.layers:
             bias = torch.randn(spec.N, generator=gen, device=dev) * 0.01 if cfg.bias else None
-            if spec.parallel == "column":
+            lora = workloads.lora_np(rng, cfg.lora_rank, spec.K, spec.N, cfg.block) if cfg.lora_rank else None
+            if spec.parallel == "column" or all_column:
                 # a rank only needs its own rows: draw them directly (N / world rows)
-                codes, scales = workloads.weight_torch(gen, spec.N // world, spec.K, dev)
-                layer = ColumnParallelLinear.__new__(ColumnParallelLinear)
-                layer.rank, layer.world, layer.slices = rank, world, [(0, spec.N // world)]
-                layer.wt = ops.QWeight("q8", gpu.wrap(codes), gpu.wrap(scales), spec.N // world, spec.K,
-                                       bias=gpu.wrap(bias[:spec.N // world].contiguous()) if bias is not None else None)
-                layer.gpu, layer.M, layer.block, layer.swiglu_in, layer.m_pad = gpu, M, cfg.block, spec.swiglu_in, m_pad
-                layer.a8, layer.sa = gpu.empty((m_pad, spec.K), "i8"), gpu.empty((m_pad,), "f32")
-                layer.out = gpu.empty((m_pad, spec.N // world), "bf16")
+                n_local = spec.N // world
+                codes, scales = workloads.weight_torch(gen, n_local, spec.K, dev)
+                splits = [spec.N // 2, spec.N // 2] if (not all_column and spec.name == "w1w3") else None
+                layer = ColumnParallelLinear(gpu, group, codes, scales, bias[:n_local].contiguous() if bias is not None else None,
+                                             M, block=cfg.block, splits=splits, swiglu_in=spec.swiglu_in and not all_column,
+                                             lora=lora, scratch=self.scratch, n_total=spec.N)
+                # with all_column a layer fed by swiglu reads its own (already activated) full-width input instead
                 x = workloads.activations_torch(gen, m_pad, spec.K, cfg.n_outliers(spec.K), dev)
                 self.inputs.append(gpu.wrap(x))
             else:
+                if lora is not None:
+                    raise ValueError("a low-rank term on a row-parallel layer is not supported")
                 codes, scales = workloads.weight_torch(gen, spec.N, spec.K, dev)
                 layer = RowParallelLinear(gpu, group, codes, scales, bias, M, block=cfg.block,
                                           swiglu_in=spec.swiglu_in, reduce=reduce, scatter=scatter)
@@ -375,8 +420,89 @@ class TensorParallelBlock:
                     self.inputs.append(gpu.wrap(x))
             self.layers.append(layer)
 
+    def _result(self, i: int):
+        """What this rank hands back to the host: its N / p columns of a column-parallel layer; its own M / p rows of
+        a row-parallel layer (every rank holds the whole reduced output; together the ranks return it once)."""
+        layer = self.layers[i]
+        out = layer.out.torch()
+        if isinstance(layer, RowParallelLinear) and not layer.scatter and self.world > 1:
+            rows = layer.m_pad // self.world
+            return out[self.rank * rows:(self.rank + 1) * rows]
+        return out
+
     def step(self):
         prev = None
         for layer, x in zip(self.layers, self.inputs):
             prev = layer(prev if x is None else x)
         return prev
+
+    def link_bytes(self):
+        """Bytes this rank sends over NVLink per step, per layer (0 for layers without an exchange). Push variants:
+        (p-1)/p of the partials (4 or 2 bytes an element) to the rows' owners plus, unless scatter, the owner's finished
+        rows (2 bytes) to the p-1 peers; NCCL all-reduce of int32: 2 (p-1)/p of 4 bytes an element (ring or tree on
+        the wire; the in-switch reduction sends every byte once)."""
+        out, p = [], self.world
+        for layer in self.layers:
+            if not isinstance(layer, RowParallelLinear) or p == 1:
+                out.append(0)
+                continue
+            mn = layer.m_pad * layer.wt.N
+            if layer.push:
+                b = (4 if layer.stage_dtype == "i32" else 2) * mn * (p - 1) // p
+                if not layer.scatter:
+                    b += 2 * mn * (p - 1) // p
+            else:
+                esize = {"int32": 4, "f32": 4, "bf16": 2}[layer.reduce]
+                b = esize * mn * (p - 1) // p * (1 if layer.scatter else 2)
+            out.append(b)
+        return out
+
+    def close(self):
+        for layer in self.layers:
+            if hasattr(layer, "close"):
+                layer.close()
+
+
+def check_sharded_chain(gpu: Gpu, group, reduce: str = "push", seed: int = 5) -> dict:
+    """A small column-parallel -> row-parallel chain (value | gate up-projection, swiglu quantiser, down-projection)
+    on this group against the SAME chain computed by this rank alone, bit for bit: the column-parallel outputs, the
+    whole-row scales, this rank's K-shard of the int8 codes, and the reduced output. Every rank draws the same seeded
+    data. Returns {"exact": bool, "failed": [names]}; collective, call on every rank."""
+    dist = _dist()
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    M, D, F, B = 1024, 1024, 2048, 128
+    rng = np.random.default_rng(seed)
+    from . import quant
+    x = quant.bf16_bits((rng.standard_normal((M, D)) * 2).astype(np.float32))
+    w_up = rng.integers(-127, 128, size=(2 * F, D), dtype=np.int8)
+    s_up = rng.uniform(1e-3, 2e-3, size=2 * F).astype(np.float32)
+    b_up = (rng.standard_normal(2 * F) * 0.01).astype(np.float32)
+    w_dn = rng.integers(-127, 128, size=(D, F), dtype=np.int8)
+    s_dn = rng.uniform(1e-3, 2e-3, size=D).astype(np.float32)
+    b_dn = (rng.standard_normal(D) * 0.01).astype(np.float32)
+    up = ColumnParallelLinear(gpu, group, w_up, s_up, b_up, M, block=B, splits=[F, F])
+    down = RowParallelLinear(gpu, group, w_dn, s_dn, b_dn, M, block=B, swiglu_in=True, reduce=reduce)
+    xs = gpu.upload(x, "bf16")
+    h_local = up(xs)
+    y = down(h_local)
+    gpu.wait()
+    full_up = ops.QWeight("q8", gpu.upload(w_up), gpu.upload(s_up), 2 * F, D, bias=gpu.upload(b_up))
+    full_dn = ops.QWeight("q8", gpu.upload(w_dn), gpu.upload(s_dn), D, F, bias=gpu.upload(b_dn))
+    a8, sa, h = gpu.empty((M, D), "i8"), gpu.empty((M,), "f32"), gpu.empty((M, 2 * F), "bf16")
+    ops.rot_q8(gpu, xs, a8, sa, M, D, block=B)
+    ops.gemm(gpu, a8, full_up, h, M, sa=sa, tile=(128, 32, 4))
+    a8b, sab, y1 = gpu.empty((M, F), "i8"), gpu.empty((M,), "f32"), gpu.empty((M, D), "bf16")
+    ops.rot_q8(gpu, h, a8b, sab, M, F, swiglu=True, block=B)
+    ops.gemm(gpu, a8b, full_dn, y1, M, sa=sab, tile=(128, 32, 4))
+    gpu.wait()
+    hh = h.numpy()
+    half = F // world
+    checks = {
+        "column-parallel output": np.array_equal(h_local.numpy(), np.concatenate([hh[:, a:b] for a, b in up.slices], axis=1)),
+        "whole-row scales": np.array_equal(down.sa.numpy(), sab.numpy()),
+        "K-shard codes": np.array_equal(down.a8.numpy(), a8b.numpy()[:, rank * half:(rank + 1) * half]),
+        "row-parallel output": np.array_equal(y.numpy(), y1.numpy()),
+    }
+    down.close()
+    failed = [k for k, ok in checks.items() if not ok]
+    return {"exact": not failed, "failed": failed}

@@ -222,15 +222,26 @@ H3B_API int h3b_reduce_dequant_gated(h3b_ctx *ctx, const void *stage, int64_t sl
  * buffer of M x R fp16 values; this entry point brings its own: T lives in a static device array inside the library
  * image, H3B_NOALLOC_MAX_T_VALUES fp16 values (8 MiB), which every GPU that loads the library holds until the
  * process exits. The call performs no cudaMalloc, cudaFree or other allocating call, and its TMA descriptors are
- * built on the stack.
+ * built on the stack. h3b_open() looks the array up on its device (which also makes the CUDA runtime load this
+ * library's device code and place the 8 MiB there, at set-up, where the context allocates anyway), so a caller that
+ * opened its context before handing HBM to its own allocator meets no implicit allocation later. One caveat remains
+ * outside the library's control: with CUDA's default lazy loading the two product kernels are loaded on their first
+ * launch, so the FIRST call per device may still load code; run one warm-up call at set-up (or set
+ * CUDA_MODULE_LOADING=EAGER) and the guarantee holds from the second call on.
+ *
+ * Size limit in practice: M x R <= 4 Mi values, e.g. 32768 rows at rank 128 or 65536 rows at rank 64. The largest
+ * benchmark configuration (66560 rows, rank 64 = 4.06 Mi values) is just above it: feed it as two row slices
+ * (any split into multiples of 128 rows; rows are independent).
  *
  * It computes T = fp16((A x lora_A^T) * sa[m] * lora_sw[j]) into that array and then the same product as
  * h3b_gemm_w8a8 with lora_T pointing at it; arguments as there, except that the term's input side is passed as its
  * int8 codes lora_A [R][la_stride] and fp32 scales lora_sw [R] (what ops.low_rank() stores) instead of a finished T.
  * Returns non-zero with a message if M x R exceeds H3B_NOALLOC_MAX_T_VALUES.
  *
- * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
- * outside any stream capture. All calls on a device share the one array and each overwrites the part it uses in
+ * The array's device address is looked up (cudaGetSymbolAddress) in h3b_open(); should a context ever reach this
+ * call without it, the first call on that device does the look-up itself, so make that first call outside any
+ * stream capture. Every argument of both products is checked before the first launch: a refused call launches
+ * nothing and leaves the array as it was. All calls on a device share the one array and each overwrites the part it uses in
  * full: calls that overlap on the GPU (two streams, two contexts on the same device) race on it - keep them on one
  * stream or order them yourself. */
 #define H3B_NOALLOC_MAX_T_VALUES (4u << 20)
@@ -261,6 +272,17 @@ H3B_API int h3b_rot_set_policy(h3b_ctx *ctx, int threads_target, int tma_stages,
  * that waits about a millisecond on a barrier nothing signals, so that exactly that happens. The counterpart of a
  * failed command buffer surfacing from h3_wait (src/capi.h:66-70, src/capi.mm:235-243). Returns 0 (the launch). */
 H3B_API int h3b_selftest_expire_wait(h3b_ctx *ctx);
+
+/* Issue-rate probe of the int8 tensor pipe: the measured ceiling the product's fractions are quoted against.
+ * Counterpart of the reference's register-fed matrix-unit probe (bench/hw/mma_rate.py:9-24, bench/hw/mma_rate.metal),
+ * whose figure is the "peak" of every percentage the reference publishes (README.md:271-273). One CTA per SM issues
+ * `iters` x 4 tcgen05.mma kind::i8 instructions of 128 x 256 x 32 (pair = 0) or, per CTA pair, 256 x 256 x 32 with
+ * cta_group::2 (pair = 1) on operand tiles that stay in shared memory, alternating between two int32 accumulators in
+ * tensor memory; no TMA, no epilogue; one bounded wait at the end. Blocking (it synchronises the context's stream and
+ * allocates a small result buffer). out[0] = seconds of the launch (CUDA events), out[1] = cycles of the slowest CTA
+ * (clock64), out[2] = multiply-add operations (2 per MAC) per clock and SM, out[3] = TOP/s over the CTAs that ran,
+ * out[4] = CTAs that ran. Returns 0 on success. */
+H3B_API int h3b_mma_rate_probe(h3b_ctx *ctx, int pair, int iters, double out[5]);
 
 /* Nothing is deferred on CUDA, so commit only exists for interface parity. Replaces h3_commit (src/capi.h:65). */
 H3B_API void h3b_commit(h3b_ctx *ctx);

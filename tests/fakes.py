@@ -147,10 +147,13 @@ class SharedPeerGpu(OracleBackedGpu):
     a row-parallel layer: a "device address" is the address of the mapping in this process, exactly as a CUDA IPC
     mapping has a different address in every process. The rendezvous is a gloo barrier."""
 
-    def __init__(self, group=None, tile_n=None):
+    def __init__(self, group=None, tile_n=None, sync_limit_s=20.0):
         super().__init__(tile_n)
         self.group = group
         self._regions = []  # (address, nbytes, uint8 array, path or None)
+        self.sync_limit_s = sync_limit_s  # how long a rendezvous polls before it gives up (the device's is ~1 s)
+        self.drop_signals = 0             # the next n rendezvous of this rank signal nobody (a message that is lost)
+        self.status = 0                   # the context's status word: 7 after a rendezvous that ran out
 
     def _register(self, arr, path=None):
         self._regions.append((arr.ctypes.data, arr.nbytes, arr, path))
@@ -168,6 +171,11 @@ class SharedPeerGpu(OracleBackedGpu):
         return t
 
     def wait(self):
+        """Like the library's h3b_wait: reports a device-side give-up once, clears it, and the context stays usable."""
+        if self.status:
+            code, self.status = self.status, 0
+            raise gpu_mod.GpuError(f"GPU kernel gave up: status {code}: rendezvous of a row-parallel layer timed out: "
+                                   f"another GPU did not signal")
         return 0.0
 
     def peer_alloc(self, nbytes):
@@ -194,12 +202,24 @@ class SharedPeerGpu(OracleBackedGpu):
         os.unlink(path)
 
     def peer_sync_native(self, flags, rank, world, epoch, mode=0):
-        import torch.distributed as dist
+        """The device protocol on the file-backed blocks: store `epoch` into word `rank` of every rank's flag array,
+        then poll this rank's own array until every word has reached `epoch` - for a bounded time, after which the
+        status word gets code 7 and the call returns (peer_sync_kernel in csrc/peer.cu)."""
+        import time
         assert mode == 0 and len(flags) == world
-        for _, _, arr, path in self._regions:
-            if path is not None or isinstance(arr, np.memmap):
-                arr.flush()
-        dist.barrier(group=self.group)
+        if self.drop_signals > 0:
+            self.drop_signals -= 1
+        else:
+            for q in range(world):
+                self._bytes(flags[q], 4 * world).view(np.uint32)[rank] = epoch
+        mine = self._bytes(flags[rank], 4 * world).view(np.uint32)
+        t0 = time.monotonic()
+        while any(int(np.int32(np.uint32(int(mine[q]) - epoch & 0xFFFFFFFF))) < 0 for q in range(world)):
+            if time.monotonic() - t0 > self.sync_limit_s:
+                if not self.status:
+                    self.status = 7
+                return
+            time.sleep(0.0005)
 
     def rot_amax_push_native(self, x, x_stride, dst, M, D, block, mode):
         amax = np.abs(self._rotated(x, x_stride, M, D, block, mode)).max(axis=1).astype(np.float32)
@@ -227,6 +247,8 @@ class SharedPeerGpu(OracleBackedGpu):
     def reduce_dequant_gated_native(self, stage_ptr, slot_stride, stage_stride, stage_dtype, world, sa_ptr, sw, bias, x,
                                     c_stride, rows, N, row0, rtype_ptr, gate, g_stride):
         from oracle import gemm_ref
+        if self.status:
+            return  # as reduce_dequant_kernel: nothing is stored after a kernel before it gave up
         v = self._reduced(stage_ptr, stage_dtype, world, sa_ptr, sw, bias, rows, N)
         X = x.numpy().reshape(-1)[:rows * N].reshape(rows, N)
         types = self._bytes(rtype_ptr, rows)
@@ -237,6 +259,8 @@ class SharedPeerGpu(OracleBackedGpu):
                               out_dtype, c_stride, rows, N, row0=0):
         from oracle import gemm_ref
         assert stage_stride == N and c_stride == N and slot_stride == rows * N
+        if self.status:
+            return  # as reduce_dequant_kernel: nothing is stored after a kernel before it gave up
         v = self._reduced(stage_ptr, stage_dtype, world, sa_ptr, sw, bias, rows, N)
         bits = gemm_ref.store_as(v, out_dtype)
         osize = gpu_mod._SIZE[out_dtype]

@@ -97,12 +97,15 @@ def test_config3_33b_block(gpu, layer):
     _check_layer(gpu, cfg, cfg.layers[layer], cfg.M, 30 + layer, _rows(cfg.M, 24), cpu_weights=False)
 
 
-@pytest.mark.parametrize("layer", [1, 3])
+@pytest.mark.parametrize("layer", range(4))
 def test_config4_stress_rows_with_lora(gpu, layer):
-    """M = 66560 rows with a rank-64 term; the two widest layers are left to the benchmark (same kernels, and
-    their outputs alone are 2.4 and 4.4 GB)."""
+    """M = 66560 rows with a rank-64 term, every layer at full size (the two widest write 2.4 and 4.4 GB of output):
+    whatever the benchmark times has been checked at its real shape first, as the reference insists for its own
+    sweeps (docs/design.md:59-69)."""
+    import torch
     cfg = workloads.CONFIGS[4]
     _check_layer(gpu, cfg, cfg.layers[layer], cfg.M, 40 + layer, _rows(cfg.M, 24), cpu_weights=False)
+    torch.cuda.empty_cache()
 
 
 @pytest.mark.parametrize("K", [3072, 6144, 16384])

@@ -147,3 +147,61 @@ def test_two_ranks_reproduce_one_rank_bit_for_bit():
         # token-sharded: rows of the full result
         m0, rows, h_tok = r["tok"]
         assert (m0, rows) == (rank * M // WORLD, M // WORLD) and np.array_equal(h_tok, h[m0:m0 + rows])
+
+
+def _late_rank_worker(rank, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        from h3metal_b200.gpu import GpuError
+        from tests.fakes import SharedPeerGpu
+        g = SharedPeerGpu(sync_limit_s=1.0)
+        x, (w_up, s_up, b_up), (w_dn, s_dn, b_dn) = _inputs()
+        up = parallel.ColumnParallelLinear(g, None, w_up, s_up, b_up, M, block=BLOCK, splits=[F, F])
+        # float inputs make the layer exchange its row maxima through the process group, so the only rendezvous of a
+        # call are the two around the owner's reduction
+        h32 = g.upload(oracle.bf16_bits_to_f32(up(g.upload(x, "bf16")).numpy()))
+        layer = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True, reduce="push")
+        first = layer(h32).numpy().copy()
+        g.wait()
+        layer.out.numpy()[...] = 0
+        dist.barrier()
+        # second step: rank 1 never joins it (a rank that stalled on the host between steps). Rank 0 runs its half
+        # alone: the quantiser's scales are given (the MAX exchange is a host-side collective that would simply
+        # block), so it goes straight to the product, the rendezvous and the reduction.
+        error = None
+        if rank == 0:
+            layer._push(g, layer.wt)
+            try:
+                g.wait()
+            except GpuError as e:
+                error = str(e)
+        dist.barrier()
+        after_failure = layer.out.numpy().copy()
+        layer.recover()
+        third = layer(h32).numpy().copy()
+        g.wait()
+        results[rank] = dict(first=first, error=error, after_failure=after_failure, third=third, rows=layer.rows)
+        layer.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_row_parallel_layer_when_one_rank_never_arrives():
+    """What a pushed row-parallel layer returns and raises when a rank never reaches the rendezvous (made on the host:
+    rank 1 sits the step out; the fake's poll is bounded like the device's). The rank that waited in vain reports the
+    give-up at wait(); its reduction stored nothing - no rank's output received sums over staging that was never
+    filled - and after recover() on both ranks the layer computes the right result again."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    results = mp.Manager().dict()
+    mp.spawn(_late_rank_worker, args=(port, results), nprocs=WORLD, join=True)
+    _, _, _, y = _single_rank_reference()
+    for rank in range(WORLD):
+        r = results[rank]
+        assert np.array_equal(r["first"], y), "before the failure"
+        assert not r["after_failure"].any(), "a reduction behind a rendezvous that ran out must store nothing"
+        assert np.array_equal(r["third"], y), "after recover()"
+    assert results[0]["error"] is not None and "did not signal" in results[0]["error"]
+    assert results[1]["error"] is None
