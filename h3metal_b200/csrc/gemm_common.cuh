@@ -31,6 +31,25 @@ __host__ __device__ constexpr int push_bytes(int bn) {
 
 __host__ __device__ constexpr int stage_bytes(int bn) { return kABytes + bn * kBKBytes; }
 
+// Position in the ring of operand stages: the stage index and the phase (parity) of its barriers' current use.
+// Stepped by hand so that the per-K-block loops of the single issuing threads need no division.
+struct RingPos {
+  uint32_t s = 0, ph = 0;
+  __device__ __forceinline__ void advance(int stages) {
+    if (++s == static_cast<uint32_t>(stages)) {
+      s = 0;
+      ph ^= 1u;
+    }
+  }
+  __device__ __forceinline__ void retreat(int stages) {
+    if (s == 0) {
+      s = static_cast<uint32_t>(stages);
+      ph ^= 1u;
+    }
+    --s;
+  }
+};
+
 struct TileCoord {
   int m_blk, n_blk;
 };

@@ -105,45 +105,51 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
   if (warp == 0) {
     // ---------------------------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      uint32_t it = 0;
+      // The ring position is a (stage, phase) pair stepped by hand: one thread issues every copy of the CTA, and at
+      // full tensor rate a K block lasts 512 cycles, so the loop must stay a few dozen instructions long (a division
+      // of a running count by the run-time stage count per K block alone costs a third of that).
+      RingPos pos;
+      uint32_t filled = 0;  // stages armed so far, saturating at `stages` (for the wind-down)
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, g.band);
         const int m0 = tc.m_blk * kBM, n0 = tc.n_blk * BN;
         if (LORA) {
-          for (int j = 0; ok && j < lora_blocks; ++j, ++it) {
-            const int s = it % stages;
-            const uint32_t ph = (it / stages) & 1u;
-            ok = mbar_wait(empty_bar(s), ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
+          for (int j = 0; ok && j < lora_blocks; ++j) {
+            ok = mbar_wait(empty_bar(pos.s), pos.ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
             if (!ok) break;
             const int n_here = min(2, chunks - 2 * j);
-            mbar_arrive_expect_tx(full_bar(s), n_here * (kLoraTBytes + kLoraBBytes));
-            const uint32_t dst = base + s * kStage;
+            const uint32_t full = full_bar(pos.s);
+            mbar_arrive_expect_tx(full, n_here * (kLoraTBytes + kLoraBBytes));
+            const uint32_t dst = base + pos.s * kStage;
             for (int c = 0; c < n_here; ++c) {
-              tma_load_2d(dst + c * kLoraTBytes, &g.map_t, full_bar(s), (2 * j + c) * kLoraChunk, m0);
-              tma_load_2d(dst + kABytes + c * kLoraBBytes, &g.map_b, full_bar(s), (2 * j + c) * kLoraChunk, n0);
+              tma_load_2d(dst + c * kLoraTBytes, &g.map_t, full, (2 * j + c) * kLoraChunk, m0);
+              tma_load_2d(dst + kABytes + c * kLoraBBytes, &g.map_b, full, (2 * j + c) * kLoraChunk, n0);
             }
+            pos.advance(stages);
+            filled += filled < static_cast<uint32_t>(stages);
           }
           if (!ok) break;
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % stages;
-          const uint32_t ph = (it / stages) & 1u;
-          ok = mbar_wait(empty_bar(s), ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(empty_bar(pos.s), pos.ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
           if (!ok) break;
-          mbar_arrive_expect_tx(full_bar(s), kStage);
-          const uint32_t dst = base + s * kStage;
-          tma_load_2d(dst, &g.map_a, full_bar(s), kb * kBKBytes, m0);
-          tma_load_2d(dst + kABytes, &g.map_w, full_bar(s), kb * kBKBytes, n0);
+          const uint32_t full = full_bar(pos.s);
+          mbar_arrive_expect_tx(full, kStage);
+          const uint32_t dst = base + pos.s * kStage;
+          tma_load_2d(dst, &g.map_a, full, kb * kBKBytes, m0);
+          tma_load_2d(dst + kABytes, &g.map_w, full, kb * kBKBytes, n0);
+          pos.advance(stages);
+          filled += filled < static_cast<uint32_t>(stages);
         }
       }
       if (*cta_abort) {
-        // wind-down: wait (bounded) for the copies this thread still has in flight
-        const uint32_t first = it > static_cast<uint32_t>(stages) ? it - stages : 0u;
-        for (uint32_t j = first; j < it; ++j) {
+        // wind-down: wait (bounded) for the copies this thread still has in flight - the last `filled` stages armed,
+        // walking back from the ring position
+        for (uint32_t j = 0; j < filled; ++j) {
+          pos.retreat(stages);
           int dummy_abort = 0;
-          mbar_wait(full_bar(j % stages), (j / stages) & 1u, &dummy_abort, g.status, kStatusDrainTimeout,
-                    kDrainLimitCycles);
+          mbar_wait(full_bar(pos.s), pos.ph, &dummy_abort, g.status, kStatusDrainTimeout, kDrainLimitCycles);
         }
       }
     }
@@ -152,7 +158,8 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
     if (lane == 0) {
       constexpr uint32_t idesc_i8 = umma_instr_desc(2, 1, kBM, BN);   // s32 accumulate, s8 x s8
       constexpr uint32_t idesc_f16 = umma_instr_desc(1, 0, kBM, BN);  // f32 accumulate, f16 x f16
-      uint32_t it = 0, at = 0;
+      uint32_t at = 0;
+      RingPos pos;
       bool ok = true;
       // operand descriptors of stage 0; stage s adds s * kStage bytes (in 16-byte units) to the address field
       const uint64_t ad0 = umma_smem_desc(base, 1024, 2);
@@ -172,10 +179,9 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
             k1 = g.ranges[2 * tc.n_blk + 1];
           }
           const uint32_t d_low = tmem_base + kLowBase + as * BN;
-          for (int j = 0; ok && j < lora_blocks; ++j, ++it) {
-            const int s = it % stages;
-            const uint32_t ph = (it / stages) & 1u;
-            ok = mbar_wait(full_bar(s), ph, cta_abort, g.status, kStatusMmaTimeout);
+          for (int j = 0; ok && j < lora_blocks; ++j) {
+            const int s = pos.s;
+            ok = mbar_wait(full_bar(s), pos.ph, cta_abort, g.status, kStatusMmaTimeout);
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t a_addr = base + s * kStage;
@@ -188,22 +194,28 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_w8a8_kernel(const
               umma_f16(d_low, td, bd, idesc_f16, kk != k0 ? 1u : 0u);
             }
             umma_commit(empty_bar(s));  // the stage may be refilled once these MMAs have read it
+            pos.advance(stages);
           }
           if (!ok) break;
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % stages;
-          const uint32_t ph = (it / stages) & 1u;
-          ok = mbar_wait(full_bar(s), ph, cta_abort, g.status, kStatusMmaTimeout);
+        // The issue loop is kept to a few dozen instructions per K block (no division, descriptors by one multiply
+        // of the stage index): one thread feeds the tensor core, and four MMAs last only 512 cycles.
+        uint32_t accumulate = 0;  // the tile's first instruction overwrites the accumulator
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const uint32_t s = pos.s;
+          ok = mbar_wait(full_bar(s), pos.ph, cta_abort, g.status, kStatusMmaTimeout);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint64_t ad = ad0 + static_cast<uint64_t>(s) * (kStage >> 4);
-          const uint64_t bd = bd0 + static_cast<uint64_t>(s) * (kStage >> 4);
+          const uint64_t ad = ad0 + static_cast<uint64_t>(s * (kStage >> 4));
+          const uint64_t bd = bd0 + static_cast<uint64_t>(s * (kStage >> 4));
+          umma_i8(d_acc, ad, bd, idesc_i8, accumulate);
+          accumulate = 1;
 #pragma unroll
-          for (int k = 0; k < kBKBytes / 32; ++k) {  // 32 int8 of K per instruction = 32 bytes = 2 descriptor units
-            umma_i8(d_acc, ad + 2u * k, bd + 2u * k, idesc_i8, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 1; k < kBKBytes / 32; ++k) {  // 32 int8 of K per instruction = 32 bytes = 2 descriptor units
+            umma_i8_acc(d_acc, ad + 2u * k, bd + 2u * k, idesc_i8);
           }
           umma_commit(empty_bar(s));
+          pos.advance(stages);
         }
         if (!ok) break;
         umma_commit(acc_full_bar(as));

@@ -80,22 +80,24 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
   if (warp == 0) {
     // ---------------------------------------------------------------------------------- TMA producer (both CTAs)
     if (lane == 0) {
-      uint32_t it = 0;
+      // ring position stepped by hand: the loop runs once per K block (512 cycles at full tensor rate) in one thread
+      RingPos pos;
+      const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);  // the leader's full barriers, 8 bytes apart
       bool ok = true;
       for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
         const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, g.band);
         const int m0 = tc.m_blk * 256 + static_cast<int>(rank) * 128;
         const int n0 = tc.n_blk * kPairBN + static_cast<int>(rank) * 128;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % stages;
-          const uint32_t ph = (it / stages) & 1u;
-          ok = mbar_wait(empty_bar(s), ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const uint32_t s = pos.s;
+          ok = mbar_wait(empty_bar(s), pos.ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
           if (!ok) break;
           if (leader) mbar_arrive_expect_tx(full_bar(s), 2u * kPairStage);
-          const uint32_t leader_full = map_to_cta(full_bar(s), 0);
+          const uint32_t leader_full = leader_full0 + 8u * s;
           const uint32_t dst = base + s * kPairStage;
           tma_load_2d_pair(dst, &g.map_a, leader_full, kb * kBKBytes, m0);
           tma_load_2d_pair(dst + kABytes, &g.map_w, leader_full, kb * kBKBytes, n0);
+          pos.advance(stages);
         }
       }
     }
@@ -103,8 +105,11 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
     // ---------------------------------------------------------------------------------- MMA issuer (leader only)
     if (leader && lane == 0) {
       constexpr uint32_t idesc = umma_instr_desc(2, 1, 256, kPairBN);  // s32 accumulate, s8 x s8, M 256 over the pair
-      uint32_t it = 0, at = 0;
+      uint32_t at = 0;
+      RingPos pos;
       bool ok = true;
+      const uint64_t ad0 = umma_smem_desc(base, 1024, 2);
+      const uint64_t bd0 = umma_smem_desc(base + kABytes, 1024, 2);
       for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++at) {
         const int as = at & 1;
         const uint32_t aph = (at >> 1) & 1u;
@@ -112,20 +117,20 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_acc = tmem_base + as * kPairBN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % stages;
-          const uint32_t ph = (it / stages) & 1u;
-          ok = mbar_wait(full_bar(s), ph, cta_abort, g.status, kStatusMmaTimeout);
+        uint32_t accumulate = 0;  // the tile's first instruction overwrites the accumulator
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const uint32_t s = pos.s;
+          ok = mbar_wait(full_bar(s), pos.ph, cta_abort, g.status, kStatusMmaTimeout);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t a_addr = base + s * kPairStage;
-          const uint64_t ad = umma_smem_desc(a_addr, 1024, 2);
-          const uint64_t bd = umma_smem_desc(a_addr + kABytes, 1024, 2);
+          const uint64_t ad = ad0 + static_cast<uint64_t>(s * (kPairStage >> 4));
+          const uint64_t bd = bd0 + static_cast<uint64_t>(s * (kPairStage >> 4));
+          umma_i8_pair(d_acc, ad, bd, idesc, accumulate);
+          accumulate = 1;
 #pragma unroll
-          for (int k = 0; k < kBKBytes / 32; ++k) {
-            umma_i8_pair(d_acc, ad + 2u * k, bd + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 1; k < kBKBytes / 32; ++k) umma_i8_pair(d_acc, ad + 2u * k, bd + 2u * k, idesc, 1u);
           umma_commit_pair(empty_bar(s), 3);  // both producers may refill this stage once the MMAs have read it
+          pos.advance(stages);
         }
         if (!ok) break;
         umma_commit_pair(acc_full_bar(as), 3);  // both epilogues
@@ -154,12 +159,17 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * kPairBN;
+      // two register sets: the TMEM loads of the next 32 columns are in flight while this chunk is finished
+      uint32_t acc_a[32], acc_b[32];
+      tmem_ld_32x32b_x32(t_acc, acc_a);
 #pragma unroll 1
-      for (int c = 0; c < kPairBN / 32; ++c) {
-        uint32_t acc[32];
-        tmem_ld_32x32b_x32(t_acc + c * 32, acc);
+      for (int c = 0; c < kPairBN / 32; c += 2) {
         tmem_ld_wait();
-        finish_chunk(g, acc, no_low, false, m, n0 + c * 32, sa_m, sw_s + c * 32, bias_s + c * 32, vec_ok);
+        tmem_ld_32x32b_x32(t_acc + (c + 1) * 32, acc_b);
+        finish_chunk(g, acc_a, no_low, false, m, n0 + c * 32, sa_m, sw_s + c * 32, bias_s + c * 32, vec_ok);
+        tmem_ld_wait();
+        if (c + 2 < kPairBN / 32) tmem_ld_32x32b_x32(t_acc + (c + 2) * 32, acc_a);
+        finish_chunk(g, acc_b, no_low, false, m, n0 + (c + 1) * 32, sa_m, sw_s + (c + 1) * 32, bias_s + (c + 1) * 32, vec_ok);
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -256,7 +256,8 @@ H3B_API int h3b_gemm_w8a8_lora_noalloc(h3b_ctx *ctx, const int8_t *A, int64_t a_
 H3B_API int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int lora);
 /* Overrides the product's choices: tile_n (0 = automatic; 32, 64, 128, 256: single-CTA tiles of that width), band
  * (row tiles swept per column tile, 0 = automatic) and pair (CTA pairs computing 256 x 256 tiles with
- * tcgen05.mma cta_group::2: 1 = whenever no low-rank term is attached; 0 or -1 = never, the default). The
+ * tcgen05.mma cta_group::2: 0 = automatic - pairs for products of at least 256 x 256 outputs without a low-rank term
+ * -, 1 = whenever no low-rank term is attached, -1 = never: 128-row single-CTA tiles). The
  * counterpart of the tile= and swz= arguments of h3metal/ops.py:124-126. Returns 0. */
 H3B_API int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band, int pair);
 /* Tuning of the rotate+quantise kernel. tma_stages: rows a CTA keeps in flight in shared memory (1..4), 0 =
