@@ -85,6 +85,8 @@ struct h3b_ctx {
   int tile_n_override = 0, band_override = 0, pair_mode = 0, rot_threads = 0, rot_stages = 0, rot_chunk = 0;
   int overlap = 0;  // programmatic dependent launch of the path's two main kernels (h3b_set_launch_overlap)
   int pair_stages = 0, pair_clusters = 0;  // CTA-pair product: ring depth and resident clusters (0 = unavailable)
+  int pair_stages_staged = 0;              // ring depth when 64 KB of shared memory stage the outputs for TMA stores
+  int store_mode = 0;                      // staged (TMA) stores of the pair product: 0 automatic, 1 whenever possible, -1 never
   uint64_t launches = 0;
   std::string name;
 
@@ -267,7 +269,8 @@ h3b_ctx *h3b_open(int device) {
   ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
   if ((e = h3b::gemm_configure(device)) != cudaSuccess) return bail("cudaFuncSetAttribute(max dynamic shared memory)", e);
   if ((e = h3b::gemm_pair_configure()) != cudaSuccess) return bail("cudaFuncSetAttribute(max dynamic shared memory)", e);
-  ctx->pair_stages = h3b::gemm_pair_pick_stages(ctx->prop.sharedMemPerBlockOptin);
+  ctx->pair_stages = h3b::gemm_pair_pick_stages(ctx->prop.sharedMemPerBlockOptin, false);
+  ctx->pair_stages_staged = h3b::gemm_pair_pick_stages(ctx->prop.sharedMemPerBlockOptin, true);
   ctx->pair_clusters = ctx->pair_stages >= 2 ? h3b::gemm_pair_max_clusters(ctx->pair_stages) : 0;
   cudaGetLastError();  // an occupancy query that failed must not poison the next launch check
   // the static scratch of h3b_gemm_w8a8_lora_noalloc is resolved (and thereby placed on this device) now, at set-up
@@ -468,6 +471,13 @@ int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band, int pair) {
   return 0;
 }
 
+int h3b_gemm_set_store_mode(h3b_ctx *ctx, int mode) {
+  if (!ctx) return fail("null context");
+  if (mode < -1 || mode > 1) return fail("gemm store mode: -1 (direct stores), 0 (automatic) or 1 (staged whenever possible)");
+  ctx->store_mode = mode;
+  return 0;
+}
+
 int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int /*lora*/) {
   if (ctx && ctx->tile_n_override) return ctx->tile_n_override;
   if (N <= 32) return 32;
@@ -525,10 +535,19 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
   // row-parallel push, which only the single-CTA kernel (128 x tile_n tiles) implements. Under the board's power cap
   // the saved data movement is what counts: measured on the 33B-class shapes 2.67-2.83 POPS against 2.54-2.61.
   const bool pair_fits = M >= 256 && N >= 256;
-  const bool pair = !lora && !push && ctx->pair_clusters > 0 && !ctx->tile_n_override &&
+  // a low-rank term's rank ranges come per column tile: pairs need the table of 256-column tiles
+  const bool pair = !push && ctx->pair_clusters > 0 && !ctx->tile_n_override &&
+                    (!lora || h3b_gemm_tile_n(ctx, N, 1) == 256) &&
                     (ctx->pair_mode == 1 || (ctx->pair_mode == 0 && pair_fits));
+  // Staged stores (the epilogue writes 16-bit outputs to shared memory and TMA stores them) cost two of the six ring
+  // stages. With a low-rank term - one accumulator pair, so the epilogue is not hidden behind the next tile - they are
+  // what shortens the exposed part. Without one they still win where K is short (fewer K blocks per tile to hide the
+  // stores behind: +9 % at 3072 x 3072, +1 % at K = 6144) and lose 2-3 % to the shallower ring from K = 10240 on.
+  const bool can_stage = pair && (c_dtype == H3B_BF16 || c_dtype == H3B_F16) && gate == nullptr && ctx->pair_stages_staged >= 2 &&
+                         reinterpret_cast<uintptr_t>(C) % 16 == 0 && (c_stride * 2) % 16 == 0;
+  const bool staged = can_stage && (ctx->store_mode == 1 || (ctx->store_mode == 0 && (lora || K <= 8192)));
   const int bn = pair ? 128 : h3b_gemm_tile_n(ctx, N, lora);  // rows of W one CTA stages per K block
-  const int stages = pair ? ctx->pair_stages
+  const int stages = pair ? (staged ? ctx->pair_stages_staged : ctx->pair_stages)
                           : h3b::gemm_pick_stages(bn, lora ? R : 0, ctx->prop.sharedMemPerBlockOptin, push);
   if (stages < 2) return fail("gemm: tile does not fit the device's shared memory");
 
@@ -546,6 +565,15 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
     if (!(m = ctx->map2(cached_maps, &local, lora_B, h3b::kDtypeF16, R, N, b_stride * 2, 32, bn, 64))) return -1;
     g.map_b = *m;
   }
+  // One accumulator pair leaves a low-rank product's epilogue exposed: sixteen warps (four per TMEM lane quarter, 64
+  // columns each) read the accumulators out in a quarter of the time four would take. Measured on M = 66560,
+  // 6144 -> 18432, rank 64, single launches: 6.11 / 5.95 / 5.25 ms with 4 / 8 / 16 warps against 4.7 ms without a term.
+  g.epi_warps = (pair && lora) ? 16 : 4;
+  if (staged) {
+    if (!(m = ctx->map2(cached_maps, &local, C, c_dtype, N, M, c_stride * 2, 64, 32, 128))) return -1;
+    g.map_c = *m;
+    g.tma_store = 1;
+  }
   if (gate != nullptr) {
     if (!rtype) return fail("gemm: the gated-residual epilogue needs the row types");
     if (c_dtype != H3B_F32) return fail("gemm: the gated-residual epilogue accumulates into an fp32 residual stream");
@@ -558,7 +586,7 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
   }
   g.sw = sw; g.sa = sa; g.bias = raw ? nullptr : bias; g.c = C; g.ranges = lora ? lora_ranges : nullptr;
   g.c_stride = c_stride; g.c_dtype = c_dtype; g.M = M; g.N = N; g.K = K; g.R = lora ? R : 0; g.bn = bn;
-  g.acc_stages = (lora && bn == 256) ? 1 : 2;
+  g.acc_stages = (lora && (bn == 256 || pair)) ? 1 : 2;
   const int tile_m = pair ? 256 : 128, tile_n = pair ? 256 : bn;
   const int m_tiles = (M + tile_m - 1) / tile_m, n_tiles = (N + tile_n - 1) / tile_n;
   int band = ctx->band_override;

@@ -113,6 +113,7 @@ struct GemmLaunch {
   CUtensorMap map_w;   // int8 [N][K], box BN x 128
   CUtensorMap map_t;   // fp16 [M][R], box 128 x 32 halves, 64-byte swizzle (LoRA only)
   CUtensorMap map_b;   // fp16 [N][R], box BN x 32 halves (LoRA only)
+  CUtensorMap map_c;   // 16-bit output [M][N] rows c_stride apart, box 32 rows x 64 columns, 128-byte swizzle (tma_store only)
   const float *sw;     // [N]
   const float *sa;     // [M]
   const float *bias;   // [N] or null
@@ -138,6 +139,8 @@ struct GemmLaunch {
   void *peer_c[kMaxPeers];
   int peer_rows;
   int overlap;         // host side: launch with programmatic stream serialization (prologue overlaps the previous kernel's tail)
+  int epi_warps;       // CTA pairs with a low-rank term: epilogue warps per CTA (4, 8 or 16)
+  int tma_store;       // CTA pairs: the epilogue stages 16-bit outputs in shared memory and TMA stores them (map_c)
 };
 
 // Shared memory a launch with this tile width and rank needs for `stages` operand stages; 0 if unsupported.
@@ -148,10 +151,11 @@ int gemm_pick_stages(int bn, int R, size_t smem_optin, bool push = false);
 cudaError_t gemm_configure(int device);  // raises the dynamic shared-memory limit of every instantiation
 cudaError_t launch_gemm_w8a8(const GemmLaunch &g, int stages, cudaStream_t stream);
 
-// CTA-pair variant (256 x 256 tile per cluster of two CTAs, no low-rank term). map_w must have a box of 128 rows
-// (each CTA stages half of the W tile); g.band counts 256-row tiles; g.bn is ignored.
-size_t gemm_pair_smem_bytes(int stages);
-int gemm_pair_pick_stages(size_t smem_optin);
+// CTA-pair variant (256 x 256 tile per cluster of two CTAs). map_w and map_b must have boxes of 128 rows (each CTA
+// stages half of the W tile and of the low-rank term's B' rows); g.band counts 256-row tiles; g.bn is ignored;
+// g.ranges, if given, holds one (k0, k1) per 256-column tile.
+size_t gemm_pair_smem_bytes(int stages, bool staged_stores);
+int gemm_pair_pick_stages(size_t smem_optin, bool staged_stores);
 cudaError_t gemm_pair_configure();
 int gemm_pair_max_clusters(int stages);
 cudaError_t launch_gemm_w8a8_pair(const GemmLaunch &g, int stages, int clusters, cudaStream_t stream);

@@ -86,6 +86,7 @@ def _signatures():
         "h3b_reduce_dequant_gated": (i32, [vp, vp, i64, i64, i32, i32, vp, vp, vp, vp, i64, i32, i32, i32, vp, vp, i64]),
         "h3b_gemm_tile_n": (i32, [vp, i32, i32]),
         "h3b_gemm_set_policy": (i32, [vp, i32, i32, i32]),
+        "h3b_gemm_set_store_mode": (i32, [vp, i32]),
         "h3b_rot_set_policy": (i32, [vp, i32, i32, i32]),
         "h3b_selftest_expire_wait": (i32, [vp]),
         "h3b_mma_rate_probe": (i32, [vp, i32, i32, ctypes.POINTER(dbl)]),
@@ -451,6 +452,11 @@ class Gpu:
 
     def gemm_tile_n(self, N: int, lora: bool) -> int:
         return lib().h3b_gemm_tile_n(self.ctx, N, int(lora))
+
+    def set_store_mode(self, mode: int = 0):
+        """How CTA pairs write 16-bit outputs: 1 staged through shared memory and TMA stores whenever possible,
+        -1 direct stores from registers, 0 automatic (staged with a low-rank term or K <= 8192)."""
+        self._check(lib().h3b_gemm_set_store_mode(self.ctx, mode))
 
     def set_policy(self, tile_n: int = 0, band: int = 0, rot_threads: int = 0, rot_stages: int = 0, pair: int = 0,
                    rot_chunk: int = 0):

@@ -260,6 +260,13 @@ H3B_API int h3b_gemm_tile_n(h3b_ctx *ctx, int N, int lora);
  * -, 1 = whenever no low-rank term is attached, -1 = never: 128-row single-CTA tiles). The
  * counterpart of the tile= and swz= arguments of h3metal/ops.py:124-126. Returns 0. */
 H3B_API int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band, int pair);
+/* How the CTA-pair product writes 16-bit outputs: 1 = staged - the epilogue converts a tile into shared memory,
+ * frees the accumulator at once and TMA stores the tile while the next one is being multiplied - whenever the output
+ * is bf16 / f16, not gated and 16-byte aligned; -1 = always with direct stores from registers; 0 = automatic
+ * (staged for products with a low-rank term, whose single accumulator pair leaves the epilogue exposed, and for
+ * products of K <= 8192, which have few K blocks per tile to hide direct stores behind).
+ * No reference counterpart. Returns 0. */
+H3B_API int h3b_gemm_set_store_mode(h3b_ctx *ctx, int mode);
 /* Tuning of the rotate+quantise kernel. tma_stages: rows a CTA keeps in flight in shared memory (1..4), 0 =
  * automatic, -1 = do not use the TMA-fed kernel. threads_target: CTA size target of the register-fed kernel that
  * serves fp32 inputs, rows over 16384 channels and tma_stages = -1 (0 = automatic). chunk: channels a thread of the

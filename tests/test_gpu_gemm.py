@@ -24,7 +24,10 @@ def _case(rng, M, N, K, full_range=True):
     return m_pad, a, w, sa, sw
 
 
-PAIR = {"single": -1, "pair": 1}  # the product on single CTAs (128-row tiles) or on CTA pairs (256 x 256 tiles)
+# the product on single CTAs (128-row tiles), on CTA pairs (256 x 256 tiles) with stores from registers, or on pairs
+# whose epilogue stages 16-bit outputs in shared memory for TMA stores
+PAIR = {"single": -1, "pair": 1, "pair-staged": 1}
+STORE = {"single": 0, "pair": -1, "pair-staged": 1}
 
 
 def _gemm(gpu, a, w, sa, sw, M, out_dtype, bias=None, tile=(64, 32, 2), variant=None, **kw):
@@ -33,12 +36,14 @@ def _gemm(gpu, a, w, sa, sw, M, out_dtype, bias=None, tile=(64, 32, 2), variant=
     out = gpu.empty((a.shape[0], N), out_dtype)
     if variant is not None:
         gpu.set_policy(pair=PAIR[variant])
+        gpu.set_store_mode(STORE[variant])
     try:
         ops.gemm(gpu, gpu.upload(a), wt, out, M, sa=gpu.upload(sa), tile=tile, **kw)
         gpu.wait()
     finally:
         if variant is not None:
             gpu.set_policy()
+            gpu.set_store_mode(0)
     return out.numpy()
 
 
@@ -96,7 +101,23 @@ def test_tile_order_does_not_change_results(gpu, band, pair):
     assert np.array_equal(got, gemm_ref.int32_product(a, w))
 
 
-@pytest.mark.parametrize("variant", ["single", "pair"])
+@pytest.mark.parametrize("M,N,K", [(200, 256, 512), (1000, 1152, 640), (2304, 2560, 1152), (130, 96, 192)])
+@pytest.mark.parametrize("out_dtype", ["f16", "bf16"])
+def test_staged_stores_write_the_same_bits(gpu, out_dtype, M, N, K):
+    """CTA pairs with the epilogue staged through shared memory and stored by TMA: ragged M, N not a multiple of the
+    256-column tile or of a 64-column panel, several tiles per CTA pair (the staging is reused). Rows beyond the
+    written count stay untouched."""
+    rng = np.random.default_rng(M + N + K)
+    m_pad, a, w, sa, sw = _case(rng, M, N, K)
+    bias = (rng.standard_normal(N) * 0.01).astype(np.float32)
+    rows = (M + 63) // 64 * 64
+    got = _gemm(gpu, a, w, sa, sw, M, out_dtype, bias=bias, variant="pair-staged")
+    stored, _, _ = gemm_ref.gemm_q8(a[:rows], w, sa[:rows], sw, bias, None, out_dtype)
+    assert np.array_equal(got[:rows], stored)
+    assert not got[rows:].any()
+
+
+@pytest.mark.parametrize("variant", ["single", "pair", "pair-staged"])
 @pytest.mark.parametrize("out_dtype", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_epilogue_matches_oracle_bit_for_bit(gpu, out_dtype, with_bias, variant):

@@ -22,14 +22,15 @@ def _block_adapter(rng, N, K):
     return A_l, B_l
 
 
-def _run(gpu, rng, M, N, K, A_l, B_l, out_dtype, tile_n=0, bias=True):
+def _run(gpu, rng, M, N, K, A_l, B_l, out_dtype, tile_n=0, bias=True, pair=0, store=0):
     m_pad = ops.pad_rows(M)
     a = rng.integers(-127, 128, size=(m_pad, K), dtype=np.int8)
     sa = rng.uniform(0.001, 0.01, size=m_pad).astype(np.float32)
     q = rng.integers(-127, 128, size=(N, K), dtype=np.int8)
     sw = (rng.uniform(0.001, 0.01, size=N) / 10).astype(np.float32)
     b = (rng.standard_normal(N) * 0.01).astype(np.float32) if bias else None
-    gpu.set_policy(tile_n, 0)
+    gpu.set_policy(tile_n, 0, pair=pair)
+    gpu.set_store_mode(store)
     try:
         scratch = ops.Scratch(gpu)
         lo = ops.low_rank(gpu, A_l, B_l, scratch)
@@ -39,6 +40,7 @@ def _run(gpu, rng, M, N, K, A_l, B_l, out_dtype, tile_n=0, bias=True):
         gpu.wait()
     finally:
         gpu.set_policy()
+        gpu.set_store_mode(0)
     term = gemm_ref.low_rank_ref(A_l, B_l)
     T = scratch.t.view((m_pad, lo.R)).numpy()
     stored, v, acc = gemm_ref.gemm_q8(a, q, sa, sw, b, term, out_dtype)
@@ -84,6 +86,38 @@ def test_dense_adapters(gpu, rank, N, K, tile_n):
     assert np.array_equal(r["T"], gemm_ref.lora_T(r["a"], r["sa"], r["term"]))
     assert rel_fro(r["got_f"][:300], r["v"][:300]) <= 1e-3
     assert rel_fro(r["got_f"][:300], r["v"][:300]) <= 1e-5  # fp32 accumulation of fp16 products: far inside the bound
+
+
+@pytest.mark.parametrize("out_dtype,store", [("f32", 0), ("bf16", -1), ("bf16", 1), ("f16", 1)])
+@pytest.mark.parametrize("rank", [32, 64, 128])
+def test_low_rank_on_cta_pairs(gpu, out_dtype, store, rank):
+    """The term inside the CTA-pair product (256 x 256 tiles, one accumulator pair), with stores from registers and
+    with the epilogue staged through shared memory; several tiles per pair, ragged M, against the oracle and against
+    the single-CTA kernel."""
+    M, N, K = 1100, 1280, 768
+    A_l = (np.random.default_rng(rank).standard_normal((rank, K)) / np.sqrt(K)).astype(np.float32)
+    B_l = (np.random.default_rng(rank + 1).standard_normal((N, rank)) * 0.5).astype(np.float32)
+    r = _run(gpu, np.random.default_rng(4), M, N, K, A_l, B_l, out_dtype, pair=1, store=store)
+    want = oracle.bf16_bits_to_f32(r["stored"]) if out_dtype == "bf16" else r["stored"].astype(np.float32)
+    assert rel_fro(r["got_f"][:M], want[:M]) <= (1e-5 if out_dtype == "f32" else 1e-3)
+    single = _run(gpu, np.random.default_rng(4), M, N, K, A_l, B_l, out_dtype, pair=-1)
+    assert rel_fro(r["got_f"][:M], single["got_f"][:M]) <= 1e-5
+    assert not r["got"][ops.pad_rows(M):].any()
+
+
+@pytest.mark.parametrize("store", [-1, 1])
+def test_rank_ranges_on_cta_pairs(gpu, store):
+    """The reference's block-structured adapter on 256-column pair tiles: tiles use only their own rank range, and the
+    columns no rank touches equal the plain product exactly."""
+    rng = np.random.default_rng(3)
+    M, N, K = 520, 1280, 512
+    A_l, B_l = _block_adapter(rng, N, K)
+    r = _run(gpu, rng, M, N, K, A_l, B_l, "bf16", bias=False, pair=1, store=store)
+    assert np.array_equal(r["T"], gemm_ref.lora_T(r["a"], r["sa"], r["term"]))
+    want = oracle.bf16_bits_to_f32(r["stored"])
+    assert rel_fro(r["got_f"][:M], want[:M]) <= 1e-3
+    plain = gemm_ref.store_as(gemm_ref.epilogue_q8(r["acc"], r["sa"], r["sw"]), "bf16")
+    assert np.array_equal(r["got"][:M, N - 128:], plain[:M, N - 128:])
 
 
 def test_term_is_not_silently_dropped(gpu):
