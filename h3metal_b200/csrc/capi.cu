@@ -591,8 +591,9 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
   const int m_tiles = (M + tile_m - 1) / tile_m, n_tiles = (N + tile_n - 1) / tile_n;
   int band = ctx->band_override;
   if (band <= 0) {
-    // keep the A band (band x tile_m rows x K bytes) well inside L2 while W streams through once per band
-    const long long budget = 24LL << 20;
+    // keep the A band (band x tile_m rows x K bytes) inside L2 while W streams through once per band; measured on
+    // M = 17408: the product is fastest with 27-36 MB bands and loses 6-15 % from 53 MB on
+    const long long budget = 32LL << 20;
     band = static_cast<int>(budget / (static_cast<long long>(tile_m) * K));
     if (band < (pair ? 2 : 4)) band = pair ? 2 : 4;
   }

@@ -59,7 +59,7 @@ def _check_layer(gpu, cfg, spec, M, seed, rows, cpu_weights):
     assert diff.max() <= 1 and (diff != 0).mean() <= 1e-4, f"{cfg.name}/{spec.name}: codes"
     if not spec.swiglu_in:
         assert diff.max() == 0 and np.array_equal(got_s, s)
-    assert np.abs(got_s.view(np.int32).astype(np.int64) - s.view(np.int32).astype(np.int64)).max() <= 4  # ulps
+    assert np.abs(got_s.view(np.int32).astype(np.int64) - s.view(np.int32).astype(np.int64)).max() <= 3  # ulps (measured worst case, swiglu rows)
     # the product is checked on the GPU's own codes so that a one-step code difference cannot hide in it
     stored, v, _ = gemm_ref.gemm_q8(got_q, codes, got_s, scales, bias, term, "bf16")
     if term is None:

@@ -2,8 +2,10 @@
 test's expectations (tests/test_ops.py:28-53: shapes D = 5376, 5120, 3072 with LayerNorm).
 
 The row statistics are fp32 sums whose order differs between implementations, so the normalising factor can differ
-in its last place: int8 codes are held to "at most 1 LSB on at most 1e-4 of the elements", scales and float outputs
-to a few ulp."""
+in its last place: int8 codes are held to "at most 1 LSB on at most 1e-4 of the elements", float outputs to 2e-6,
+and the row scales to the largest distance measured over these cases, in units in the last place: 3 for RMSNorm,
+8 for LayerNorm, where removing a mean of 50 from values of spread 3 magnifies the order of the mean's summation
+(16 over 3000 rows of 3840 channels)."""
 import numpy as np
 import pytest
 
@@ -12,6 +14,11 @@ from h3metal_b200 import ops
 from tests.conftest import rel_fro
 
 pytestmark = pytest.mark.gpu
+
+
+def ulp_distance(a, b):
+    """Distance between positive fp32 values in units in the last place (difference of their bit patterns)."""
+    return np.abs(a.astype(np.float32).view(np.int32).astype(np.int64) - b.astype(np.float32).view(np.int32).astype(np.int64))
 
 
 def _case(rng, M, D, ln, types=3):
@@ -44,7 +51,7 @@ def test_codes_scales_and_float_outputs(gpu, request, variant, M, D, ln, block):
     q, s = oracle.norm_mod_rows(x, mod, rt, D, eps=1e-5, block=block, ln=ln)
     diff = np.abs(out.numpy().astype(np.int32) - q.astype(np.int32))
     assert diff.max() <= 1 and (diff != 0).mean() <= 1e-4
-    assert np.allclose(sa.numpy(), s, rtol=1e-6)
+    assert ulp_distance(sa.numpy(), s).max() <= (8 if ln else 3)
     f = oracle.norm_mod_rows(x, mod, rt, D, eps=1e-5, block=block, ln=ln, out="f")
     assert np.allclose(of.numpy(), f, rtol=2e-6, atol=2e-6 * np.abs(f).max())
     assert rel_fro(oh.numpy(), f) < 5e-4
@@ -93,7 +100,7 @@ def test_fused_residual_update(gpu, M, D):
     assert np.allclose(got_x[:, :D], upd, rtol=2e-6, atol=2e-6 * np.abs(upd).max()) and not got_x[:, D:].any()
     diff = np.abs(out.numpy().astype(np.int32) - q.astype(np.int32))
     assert diff.max() <= 1 and (diff != 0).mean() <= 1e-4
-    assert np.allclose(sa.numpy(), s, rtol=1e-6)
+    assert ulp_distance(sa.numpy(), s).max() <= 4
 
 
 def test_feeds_the_product_like_rot_q8_does(gpu):

@@ -1,8 +1,9 @@
 """rot_q8 on the GPU (through ops.rot_q8 -> ctypes -> h3b_rot_q8) against the CPU oracle.
 
 Acceptance: int8 codes bit-exact, at most 1 LSB on at most 1e-4 of the elements; scales bit-exact without the
-silu step and within 4 units in the last place with it (exp and the division inside silu differ between math
-libraries in their last places, and the row maximum inherits that)."""
+silu step and within 3 units in the last place with it (exp and the division inside silu differ between math
+libraries in their last places, and the row maximum inherits that; 3 is the largest distance measured over these cases
+and over 5000 further rows of up to 16384 channels, every kernel variant)."""
 import numpy as np
 import pytest
 
@@ -52,7 +53,7 @@ def _check_codes(gq, gs, q, s, exact):
         assert np.array_equal(gs, s)
     else:
         assert diff.max() <= 1 and (diff != 0).mean() <= 1e-4
-        assert ulp_distance(gs, s).max() <= 4
+        assert ulp_distance(gs, s).max() <= 3
 
 
 @pytest.mark.parametrize("variant", ["tma", "tma_c32", "tma_c64", "regs"])
