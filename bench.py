@@ -331,7 +331,7 @@ def time_block(gpu, blk, cfg, M, args, timer, clocks, peak_tops=None, seconds=WI
         tops = gemm_ops / gemm_s / 1e12
         gc = clocks.summary(gspans[0][0], gspans[-1][1])
         res["roofline"] = {
-            "bound": "tensor", "kernel": "gemm_w8a8_kernel (tcgen05 kind::i8)", "achieved": tops,
+            "bound": "tensor", "kernel": "gemm_w8a8_pair_kernel (tcgen05 kind::i8, cta_group::2; 256 x 256 tiles)", "achieved": tops,
             "peak": peak_tops, "unit": "TOP/s", "frac": tops / peak_tops if peak_tops else None,
             "traffic": NCU_TRAFFIC_BYTES.get(config_number(cfg)),
             "algorithmic_bytes": sum(l.m_pad * l.wt.K + l.wt.N * l.wt.K + 2 * l.m_pad * l.wt.N for l in blk.layers) / len(blk.layers),

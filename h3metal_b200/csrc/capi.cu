@@ -724,7 +724,7 @@ int h3b_gemm_w8a8_push(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const in
 static int reduce_enqueue(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride, int stage_dtype,
                           int world, const float *sa, const float *sw, const float *bias, void *const *outs, int n_out,
                           int c_dtype, int64_t c_stride, int rows, int N, int row0, const uint8_t *rtype,
-                          const float *gate, int64_t g_stride) {
+                          const float *gate, int64_t g_stride, const float *low = nullptr, int64_t low_stride = 0) {
   if (!ctx) return fail("null context");
   if (!stage || !outs) return fail("reduce_dequant: null tensor argument");
   if (world < 1 || world > h3b::kMaxPeers || n_out < 1 || n_out > h3b::kMaxPeers) return fail("reduce_dequant: 1 to 8 slots and outputs");
@@ -740,6 +740,11 @@ static int reduce_enqueue(h3b_ctx *ctx, const void *stage, int64_t slot_stride, 
   r.stage = stage; r.slot_stride = slot_stride; r.stage_stride = stage_stride; r.stage_dtype = stage_dtype; r.world = world;
   r.sa = sa; r.sw = sw; r.bias = bias; r.n_out = n_out; r.c_stride = c_stride; r.c_dtype = c_dtype; r.rows = rows; r.N = N;
   r.row0 = row0;
+  if (low) {
+    if (low_stride < N || (low_stride * 4) % 16 || reinterpret_cast<uintptr_t>(low) % 16)
+      return fail("reduce_dequant: the low-rank term's rows must be 16-byte aligned and at least N long");
+    r.low = low; r.low_stride = low_stride;
+  }
   r.status = ctx->status_dev;
   if (gate) {
     if (!rtype) return fail("reduce_dequant (gated): null row types");
@@ -760,6 +765,15 @@ int h3b_reduce_dequant(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int
                        int c_dtype, int64_t c_stride, int rows, int N, int row0) {
   return reduce_enqueue(ctx, stage, slot_stride, stage_stride, stage_dtype, world, sa, sw, bias, outs, n_out, c_dtype,
                         c_stride, rows, N, row0, nullptr, nullptr, 0);
+}
+
+int h3b_reduce_dequant_low(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride, int stage_dtype,
+                           int world, const float *sa, const float *sw, const float *bias, const float *low,
+                           int64_t low_stride, void *const *outs, int n_out, int c_dtype, int64_t c_stride, int rows, int N,
+                           int row0, const uint8_t *rtype, const float *gate, int64_t g_stride) {
+  if (!low) return fail("reduce_dequant_low: null low-rank term");
+  return reduce_enqueue(ctx, stage, slot_stride, stage_stride, stage_dtype, world, sa, sw, bias, outs, n_out,
+                        gate ? H3B_F32 : c_dtype, c_stride, rows, N, row0, rtype, gate, g_stride, low, low_stride);
 }
 
 int h3b_reduce_dequant_gated(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride, int stage_dtype,

@@ -68,6 +68,10 @@ struct ReduceLaunch {
   long long stage_stride;   // elements between rows
   int stage_dtype, world;
   const float *sa, *sw, *bias;
+  // A low-rank term of a row-parallel layer: fp32 [rows][low_stride], added after the bias, where the product's own
+  // epilogue adds it (the owner computes it for its rows from the reduced T; see h3b_reduce_dequant_low). Or null.
+  const float *low;
+  long long low_stride;
   void *out[kMaxPeers];     // out[0] only, or one base per GPU (each [..][c_stride], rows written at row0 + m)
   int n_out;
   long long c_stride;

@@ -143,6 +143,13 @@ __global__ void __launch_bounds__(256) reduce_dequant_kernel(const __grid_consta
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = __fadd_rn(v[j], b[j]);
     }
+    if (r.low != nullptr) {  // the low-rank term joins after the bias, as in the product's epilogue
+      const float *lp = r.low + m * r.low_stride + n;
+      const float4 l0 = *reinterpret_cast<const float4 *>(lp), l1 = *reinterpret_cast<const float4 *>(lp + 4);
+      const float l[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __fadd_rn(v[j], l[j]);
+    }
     const long long dst = (static_cast<long long>(r.row0) + m) * r.c_stride + n;
     if constexpr (sizeof(OUT_T) == 4) {
       if (r.gate != nullptr) {  // X += gate[type] * v: one multiply, one add, like the product's own epilogue 1

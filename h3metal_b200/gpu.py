@@ -83,6 +83,8 @@ def _signatures():
         "h3b_gemm_w8a8_push": (i32, [vp, vp, i64, vp, i64, vp, vp, ctypes.POINTER(vp), i32, i32, i32, i64, i32, i32, i32]),
         "h3b_reduce_dequant": (i32, [vp, vp, i64, i64, i32, i32, vp, vp, vp, ctypes.POINTER(vp), i32, i32, i64, i32, i32,
                                      i32]),
+        "h3b_reduce_dequant_low": (i32, [vp, vp, i64, i64, i32, i32, vp, vp, vp, vp, i64, ctypes.POINTER(vp), i32, i32, i64, i32,
+                                         i32, i32, vp, vp, i64]),
         "h3b_reduce_dequant_gated": (i32, [vp, vp, i64, i64, i32, i32, vp, vp, vp, vp, i64, i32, i32, i32, vp, vp, i64]),
         "h3b_gemm_tile_n": (i32, [vp, i32, i32]),
         "h3b_gemm_set_policy": (i32, [vp, i32, i32, i32]),
@@ -439,6 +441,22 @@ class Gpu:
         if self._profile:
             self.names.append("reduce_dequant")
 
+    def reduce_dequant_low_native(self, stage_ptr: int, slot_stride: int, stage_stride: int, stage_dtype: str, world: int,
+                                  sa_ptr: int | None, sw: Tensor | None, bias: Tensor | None, low: Tensor, low_stride: int,
+                                  outs, out_dtype: str, c_stride: int, rows: int, N: int, row0: int = 0,
+                                  rtype_ptr: int | None = None, gate: Tensor | None = None, g_stride: int = 0):
+        """The owner's reduction with a low-rank term added after the bias; with gate, outs = [X] and the result is
+        accumulated into the fp32 residual stream."""
+        p = lambda t: t.ptr if t is not None else None  # noqa: E731
+        self._check(lib().h3b_reduce_dequant_low(self.ctx, ctypes.c_void_p(stage_ptr), slot_stride, stage_stride,
+                                                  _ABI_DTYPE[stage_dtype], world,
+                                                  ctypes.c_void_p(sa_ptr) if sa_ptr else None, p(sw), p(bias), low.ptr,
+                                                  low_stride, self._ptr_array(outs), len(outs), _ABI_DTYPE[out_dtype],
+                                                  c_stride, rows, N, row0,
+                                                  ctypes.c_void_p(rtype_ptr) if rtype_ptr else None, p(gate), g_stride))
+        if self._profile:
+            self.names.append("reduce_dequant(low)")
+
     def reduce_dequant_gated_native(self, stage_ptr: int, slot_stride: int, stage_stride: int, stage_dtype: str, world: int,
                                     sa_ptr: int | None, sw: Tensor | None, bias: Tensor | None, x: Tensor, c_stride: int,
                                     rows: int, N: int, row0: int, rtype_ptr: int, gate: Tensor, g_stride: int):
@@ -506,7 +524,11 @@ class Gpu:
             if tn != self.gemm_tile_n(N, True):
                 raise GpuError(f"gemm: the low-rank range table is for {tn}-column tiles; this library uses "
                                f"{self.gemm_tile_n(N, True)} for N={N} (build it with LowRank.table(gpu, that width))")
-            head = lr.numpy()[:2]
+            # T's and B's row strides lead the table. A table built by LowRank.table() carries them on the host; only
+            # a table from elsewhere is read back from the device (a blocking copy).
+            head = getattr(lr, "host_head", None)
+            if head is None:
+                head = lr.numpy()[:2]
             R = int(head[0])
             ranges_ptr = lr.ptr + 8
             lora_args = (lt, int(head[0]), lb, int(head[1]), R, ranges_ptr)

@@ -45,6 +45,7 @@ class Scratch:
 
     def __init__(self, gpu: Gpu):
         self.gpu, self.t, self.n = gpu, None, 0
+        self.t32, self.n32 = None, 0
 
     def get(self, rows: int, cols: int) -> Tensor:
         if rows * cols > self.n:
@@ -54,7 +55,7 @@ class Scratch:
 
     def get_i32(self, rows: int, cols: int) -> Tensor:
         """A second, int32 buffer: partial accumulators of T when its product is split along K."""
-        if rows * cols > getattr(self, "n32", 0):
+        if rows * cols > self.n32:
             self.n32 = rows * cols
             self.t32 = self.gpu.empty((self.n32,), "i32")
         return self.t32.view((rows, cols))
@@ -108,6 +109,7 @@ class LowRank:
             lo = np.where(hi > lo, lo // RANK_STEP * RANK_STEP, 0)
             hi = np.where(hi > lo, -(-hi // RANK_STEP) * RANK_STEP, 0)
             t = gpu.upload(np.concatenate([[self.R, self.R], np.stack([lo, hi], 1).reshape(-1)]).astype(np.int32))
+            t.host_head = (self.R, self.R)  # the two leading strides, for callers that would otherwise read them back
             self.tables[tn] = t
         return t
 

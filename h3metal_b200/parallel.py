@@ -26,7 +26,14 @@ row-parallel    W's columns (K) are split; the input arrives already sharded on 
                 epilogue and - unless `scatter=True` - stores the finished bf16 rows into every GPU's output. Exact
                 int32 partials cross NVLink once (reduce-scatter) and the all-gather moves 2-byte outputs, a quarter
                 less traffic than an int32 all-reduce; `push_bf16` halves the first leg again.
-                K / p must be a multiple of the rotation block. A LoRA term on a row-parallel layer is not supported.
+                K / p must be a multiple of the rotation block.
+                A LoRA term on a row-parallel layer (`lora=`, push variants with int32 staging): the term's input-side
+                product T = A' x is a product over K like the main one, so every rank multiplies its K shard of A'
+                (prepared from the whole A, hence the unsharded layer's codes and scales) and pushes the int32
+                partial sums [M][R] to the rows' owners next to the main partials; after the same rendezvous the
+                owner adds them exactly, stores T for its rows in fp16, forms T B'^T for its rows with the product
+                kernel's low-rank path (on an all-zero int8 product, whose epilogue stores 0 + low) and adds it after
+                the bias in the reduction. T is bit-identical to one GPU's at any p.
                 Failure behaviour of the push variants: the device-side rendezvous polls for about a second; when a
                 rank is late or absent the waiting rank's kernel records the give-up and returns, the reduction
                 queued behind it stores nothing (no sum over staging that was never filled reaches an output), and
@@ -223,12 +230,16 @@ class RowParallelLinear:
     swiglu_in). The output [M][N] is complete on every rank after the reduction."""
 
     def __init__(self, gpu: Gpu, group, codes, scales, bias, M: int, *, block: int = 128, swiglu_in: bool = False,
-                 out_dtype: str = "bf16", reduce: str = "int32", scatter: bool = False):
+                 out_dtype: str = "bf16", reduce: str = "int32", scatter: bool = False, lora=None,
+                 scratch: ops.Scratch | None = None):
+        """lora = (A [r][K], B [N][r]) of the WHOLE layer, A in the rotated input space (reduce="push" only)."""
         dist = _dist()
         if reduce not in ("int32", "f32", "bf16", "push", "push_bf16"):
             raise ValueError(f"reduce={reduce!r}")
         if scatter and reduce not in ("int32", "push", "push_bf16"):
             raise ValueError("scatter=True is implemented for the int32 reduction and the push variants")
+        if lora is not None and reduce != "push":
+            raise ValueError("a low-rank term on a row-parallel layer needs reduce='push' (exact int32 partial sums of T)")
         self.group, self.reduce, self.scatter = group, reduce, scatter
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         N, K = codes.shape
@@ -249,11 +260,30 @@ class RowParallelLinear:
             self.r0 = self.rank * self.rows
             # behind the staging and the output: a table of `world` slots of row maxima, for the whole-row scale
             self.amax_offset = total
-            self.block_mem = PeerBlock(gpu, group, total + self.world * self.m_pad * 4)
+            total += self.world * self.m_pad * 4
+            self.low = None
+            if lora is not None:
+                # The term is prepared from the whole A and B; this rank keeps its K shard of A's codes. Behind the
+                # maxima: two staging buffers of `world` slots [rows][R] int32 for T's partial sums.
+                A_l, B_l = lora
+                self.low = ops.low_rank(gpu, A_l, B_l, scratch or ops.Scratch(gpu))
+                R = self.low.R
+                self.low_a = ops.QWeight("q8", gpu.upload(np.ascontiguousarray(self.low.codes[:, k0:k1])), self.low.a.sw, R,
+                                         k1 - k0)
+                self.t_slot_bytes = self.rows * R * 4
+                self.t_offset = total
+                total += 2 * self.world * self.t_slot_bytes
+                self.t_rows = gpu.empty((self.rows, R), "f16")        # T of this rank's rows
+                self.low_rows = gpu.empty((self.rows, int(N)), "f32")  # T B'^T of this rank's rows
+                # an all-zero int8 product of the output's shape: its epilogue stores 0 * sa * sw + low = low
+                zero_w = ops.QWeight("q8", gpu.empty((int(N), 128), "i8"), gpu.empty((int(N),), "f32"), int(N), 128)
+                self.zero = (gpu.empty((self.rows, 128), "i8"), gpu.empty((self.rows,), "f32"), zero_w)
+            self.block_mem = PeerBlock(gpu, group, total)
             self.out_offset, self.calls = out_off, 0
             self.out = (gpu.empty((self.rows, int(N)), out_dtype) if scatter
                         else self.block_mem.view(out_off, (self.m_pad, int(N)), out_dtype))
             return
+        self.low = None
         self.out = gpu.empty((self.m_pad, int(N)), out_dtype)
         self.partial = gpu.empty((self.m_pad, int(N)), {"int32": "i32", "f32": "f32", "bf16": "bf16"}[reduce])
         if scatter:  # every rank keeps only its M / p rows of the result: half the traffic of an all-reduce
@@ -337,20 +367,48 @@ class RowParallelLinear:
         self.calls += 1
         # this rank's slot in every owner's staging buffer
         slots = [mem.addr(o, buf + self.rank * self.slot_bytes) for o in range(self.world)]
+        low = self.low
+        if low is not None:
+            # the K shard's partial sums of T = A' x, pushed to the rows' owners like the main partials (before them,
+            # so that the one rendezvous below covers both)
+            t_buf = self.t_offset + ((self.calls - 1) % 2) * self.world * self.t_slot_bytes
+            t_slots = [mem.addr(o, t_buf + self.rank * self.t_slot_bytes) for o in range(self.world)]
+            gpu.gemm_push_native(self.a8, wt.K, self.low_a.w, self.low_a.w_stride, None, None, t_slots, self.rows, "i32",
+                                 low.R, self.m_pad, low.R, wt.K)
         gpu.gemm_push_native(self.a8, wt.K, wt.w, wt.w_stride, wt.sw, self.sa, slots, self.rows, self.stage_dtype, N,
                              self.m_pad, N, wt.K)
         mem.sync()  # every rank's partials of my rows have landed
         esize = 4 if self.stage_dtype == "i32" else 2
+        sa_rows = self.sa.ptr + 4 * self.r0
+        if low is not None:
+            # T of my rows: the exact sum of the shards' partial sums, then T's own epilogue (fp16 store); the term of
+            # my rows from the product kernel's low-rank path on an all-zero product
+            gpu.reduce_dequant_native(mem.addr(self.rank, t_buf), self.t_slot_bytes // 4, low.R, "i32", self.world, sa_rows,
+                                      low.a.sw, None, [self.t_rows.ptr], "f16", low.R, self.rows, low.R)
+            a0, sa0, w0 = self.zero
+            gpu.gemm_native(a0, 128, w0.w, 128, w0.sw, sa0, None, self.low_rows, "f32", N, self.rows, N, 128,
+                            self.t_rows, low.R, low.b, low.R, low.R, low.table(gpu, gpu.gemm_tile_n(N, True)).ptr + 8,
+                            name="gemm(low-rank term of my rows)")
         if gated is not None:
             X, rtype, gate, g_stride = gated
+            if low is not None:
+                gpu.reduce_dequant_low_native(mem.addr(self.rank, buf), self.slot_bytes // esize, N, self.stage_dtype,
+                                              self.world, sa_rows, wt.sw, self.bias, self.low_rows, N, [X.ptr], "f32", N,
+                                              self.rows, N, 0, rtype.ptr, gate, g_stride)
+                return X
             gpu.reduce_dequant_gated_native(mem.addr(self.rank, buf), self.slot_bytes // esize, N, self.stage_dtype,
-                                            self.world, self.sa.ptr + 4 * self.r0, wt.sw, self.bias, X, N, self.rows, N, 0,
+                                            self.world, sa_rows, wt.sw, self.bias, X, N, self.rows, N, 0,
                                             rtype.ptr, gate, g_stride)
             return X
         outs = [self.out.ptr] if self.scatter else [mem.addr(q, self.out_offset) for q in range(self.world)]
-        gpu.reduce_dequant_native(mem.addr(self.rank, buf), self.slot_bytes // esize, N, self.stage_dtype, self.world,
-                                  self.sa.ptr + 4 * self.r0, wt.sw, self.bias, outs, self.out.dtype, N, self.rows, N,
-                                  row0=0 if self.scatter else self.r0)
+        if low is not None:
+            gpu.reduce_dequant_low_native(mem.addr(self.rank, buf), self.slot_bytes // esize, N, self.stage_dtype,
+                                          self.world, sa_rows, wt.sw, self.bias, self.low_rows, N, outs, self.out.dtype, N,
+                                          self.rows, N, row0=0 if self.scatter else self.r0)
+        else:
+            gpu.reduce_dequant_native(mem.addr(self.rank, buf), self.slot_bytes // esize, N, self.stage_dtype, self.world,
+                                      sa_rows, wt.sw, self.bias, outs, self.out.dtype, N, self.rows, N,
+                                      row0=0 if self.scatter else self.r0)
         if not self.scatter:
             mem.sync()  # every rank's finished rows have landed in my output
         return self.out
@@ -408,11 +466,10 @@ class TensorParallelBlock(HostStaged):
                 x = workloads.activations_torch(gen, m_pad, spec.K, cfg.n_outliers(spec.K), dev)
                 self.inputs.append(gpu.wrap(x))
             else:
-                if lora is not None:
-                    raise ValueError("a low-rank term on a row-parallel layer is not supported")
                 codes, scales = workloads.weight_torch(gen, spec.N, spec.K, dev)
                 layer = RowParallelLinear(gpu, group, codes, scales, bias, M, block=cfg.block,
-                                          swiglu_in=spec.swiglu_in, reduce=reduce, scatter=scatter)
+                                          swiglu_in=spec.swiglu_in, reduce=reduce, scatter=scatter, lora=lora,
+                                          scratch=self.scratch)
                 if spec.swiglu_in:
                     self.inputs.append(None)  # the previous (column-parallel) layer's local value | gate output
                 else:

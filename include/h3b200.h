@@ -202,6 +202,18 @@ H3B_API int h3b_gemm_w8a8_push(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, 
 H3B_API int h3b_reduce_dequant(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride,
                                int stage_dtype, int world, const float *sa, const float *sw, const float *bias,
                                void *const *outs, int n_out, int c_dtype, int64_t c_stride, int rows, int N, int row0);
+/* The owner's reduction for a row-parallel layer that carries a low-rank term: as h3b_reduce_dequant (gate == NULL) or
+ * h3b_reduce_dequant_gated (gate != NULL; c_dtype is then ignored and outs[0] is X), with low[m][n] - fp32
+ * [rows][low_stride], the owner's rows of T B'^T - added after the bias, where the product's own epilogue adds the
+ * term (kernels/gemm.metal:251-253). The owner obtains T for its rows from the K shards' int32 partial sums of the
+ * term's input-side product, pushed and reduced like the main product's, and the term itself from one call of
+ * h3b_gemm_w8a8 on an all-zero int8 product with that T (the epilogue then stores 0 * sa * sw + low). No reference
+ * counterpart (single GPU). */
+H3B_API int h3b_reduce_dequant_low(h3b_ctx *ctx, const void *stage, int64_t slot_stride, int64_t stage_stride,
+                                   int stage_dtype, int world, const float *sa, const float *sw, const float *bias,
+                                   const float *low, int64_t low_stride, void *const *outs, int n_out, int c_dtype,
+                                   int64_t c_stride, int rows, int N, int row0, const uint8_t *rtype, const float *gate,
+                                   int64_t g_stride);
 /* The owner's reduction with the reference's second epilogue (EPI 1, kernels/gemm.metal:18-20,256-259), for the
  * attention-out and FFN-down projections of models that accumulate into an fp32 residual stream: with v the value
  * h3b_reduce_dequant would store,  X[row0 + m][n] += gate[rtype[m]][n] * v  for the owner's rows; X fp32

@@ -125,14 +125,17 @@ class OracleBackedGpu(RecordingGpu):
     def gemm_native(self, a, a_stride, w, w_stride, sw, sa, bias, out, out_dtype, c_stride, M, N, K, lt=None,
                     t_stride=0, lb=None, b_stride=0, R=0, ranges_ptr=None, name="gemm"):
         from oracle import gemm_ref
-        assert lt is None, "the fake does not carry the low-rank term"
         acc = gemm_ref.int32_product(self._rows(a, M, K, a_stride, "i8"), self._rows(w, N, K, w_stride, "i8"))
         dst = self._rows(out, M, N, c_stride, out_dtype)
         if out_dtype == "i32":
             dst[...] = acc
             return
+        low = None
+        if lt is not None:  # T B'^T as the oracle forms it (fp16 inputs, wide accumulation; gemm_ref.lora_low)
+            T = self._rows(lt, M, R, t_stride, "f16").astype(np.float64)
+            low = (T @ self._rows(lb, N, R, b_stride, "f16").astype(np.float64).T).astype(np.float32)
         v = gemm_ref.epilogue_q8(acc, sa.numpy().reshape(-1)[:M], sw.numpy().reshape(-1)[:N],
-                                 bias.numpy().reshape(-1)[:N] if bias is not None else None)
+                                 bias.numpy().reshape(-1)[:N] if bias is not None else None, low)
         dst[...] = gemm_ref.store_as(v, out_dtype)
 
     def dequant_native(self, acc, acc_stride, sa, sw, bias, out, c_stride, M, N):
@@ -255,6 +258,22 @@ class SharedPeerGpu(OracleBackedGpu):
         table = gate.numpy().reshape(-1, g_stride)[:, :N]
         X[...] = gemm_ref.accumulate_gated(X, v, table, types)
 
+    def reduce_dequant_low_native(self, stage_ptr, slot_stride, stage_stride, stage_dtype, world, sa_ptr, sw, bias, low,
+                                  low_stride, outs, out_dtype, c_stride, rows, N, row0=0, rtype_ptr=None, gate=None,
+                                  g_stride=0):
+        from oracle import gemm_ref
+        assert low_stride == N
+        if self.status:
+            return
+        term = low.numpy().reshape(-1)[:rows * N].reshape(rows, N)
+        v = self._reduced(stage_ptr, stage_dtype, world, sa_ptr, sw, bias, rows, N, term)
+        if gate is not None:
+            X = self._bytes(outs[0], rows * N * 4).view(np.float32).reshape(rows, N)
+            table = gate.numpy().reshape(-1, g_stride)[:, :N]
+            X[...] = gemm_ref.accumulate_gated(X, v, table, self._bytes(rtype_ptr, rows))
+            return
+        self._store_rows(gemm_ref.store_as(v, out_dtype), outs, out_dtype, rows, N, row0)
+
     def reduce_dequant_native(self, stage_ptr, slot_stride, stage_stride, stage_dtype, world, sa_ptr, sw, bias, outs,
                               out_dtype, c_stride, rows, N, row0=0):
         from oracle import gemm_ref
@@ -262,20 +281,24 @@ class SharedPeerGpu(OracleBackedGpu):
         if self.status:
             return  # as reduce_dequant_kernel: nothing is stored after a kernel before it gave up
         v = self._reduced(stage_ptr, stage_dtype, world, sa_ptr, sw, bias, rows, N)
-        bits = gemm_ref.store_as(v, out_dtype)
+        self._store_rows(gemm_ref.store_as(v, out_dtype), outs, out_dtype, rows, N, row0)
+
+    def _store_rows(self, bits, outs, out_dtype, rows, N, row0):
         osize = gpu_mod._SIZE[out_dtype]
         for o in outs:
             dst = self._bytes(o + row0 * N * osize, rows * N * osize)
             dst.view(gpu_mod._NP[out_dtype]).reshape(rows, N)[...] = bits
 
-    def _reduced(self, stage_ptr, stage_dtype, world, sa_ptr, sw, bias, rows, N):
+    def _reduced(self, stage_ptr, stage_dtype, world, sa_ptr, sw, bias, rows, N, low=None):
         from oracle import bf16_bits_to_f32, gemm_ref
         esize = 4 if stage_dtype == "i32" else 2
         stage = self._bytes(stage_ptr, world * rows * N * esize)
         b = bias.numpy().reshape(-1)[:N] if bias is not None else None
         if stage_dtype == "i32":
             acc = stage.view(np.int32).reshape(world, rows, N).sum(axis=0, dtype=np.int32)
-            return gemm_ref.epilogue_q8(acc, self._bytes(sa_ptr, rows * 4).view(np.float32), sw.numpy().reshape(-1)[:N], b)
+            return gemm_ref.epilogue_q8(acc, self._bytes(sa_ptr, rows * 4).view(np.float32), sw.numpy().reshape(-1)[:N], b,
+                                        low)
+        assert low is None
         parts = bf16_bits_to_f32(stage.view(np.uint16).reshape(world, rows, N))
         v = np.zeros((rows, N), np.float32)
         for s in range(world):

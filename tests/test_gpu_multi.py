@@ -93,6 +93,26 @@ layer.accumulate_gated(h_local, X, g.upload(types[r0:r0 + rows]), g.upload(gates
 g.wait()
 assert np.array_equal(X.numpy(), X1.numpy()[r0:r0 + rows]), "gated accumulate on the owner's rows"
 layer.close()
+# a LoRA term on the row-parallel layer: T of the owner's rows is one GPU's T bit for bit (exact int32 partial sums
+# over the K shards); the output differs from one GPU's only by where the term's fp32 MMAs ran
+A_d = (rng.standard_normal((40, F)) / np.sqrt(F)).astype(np.float32)
+B_d = (rng.standard_normal((D, 40)) * 0.5).astype(np.float32)
+scr = ops.Scratch(g)
+full_dl = ops.QWeight("q8", g.upload(w_dn), g.upload(s_dn), D, F, bias=g.upload(b_dn), low=ops.low_rank(g, A_d, B_d, scr))
+y_l1 = g.empty((M, D), "bf16")
+ops.gemm(g, a8b, full_dl, y_l1, M, sa=sab, tile=(128, 32, 4))
+g.wait()
+T1 = scr.t.view((M, 64)).numpy().copy()
+assert not np.array_equal(y_l1.numpy(), y1.numpy()), "the LoRA term changes the output"
+layer = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=B, swiglu_in=True, reduce="push", lora=(A_d, B_d))
+for call in range(2):
+    y_l = layer(h_local)
+    g.wait()
+    assert np.array_equal(layer.t_rows.numpy(), T1[r0:r0 + rows]), "T of the owner's rows"
+    a, b = oracle.bf16_bits_to_f32(y_l.numpy()), oracle.bf16_bits_to_f32(y_l1.numpy())
+    rel = np.linalg.norm(a - b) / np.linalg.norm(b)
+    assert rel <= 1e-5, ("row-parallel LoRA", call, rel)
+layer.close()
 dist.barrier(); dist.destroy_process_group()
 print(f"rank {rank} ok")
 '''

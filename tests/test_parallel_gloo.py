@@ -50,6 +50,14 @@ def _inputs():
     return x, (w_up, s_up, b_up), (w_dn, s_dn, b_dn)
 
 
+def _adapter(rank=24):
+    """A rank-24 adapter of the down projection (A in the rotated input space), rounded up to 32 ranks when stored."""
+    rng = np.random.default_rng(11)
+    A_l = (rng.standard_normal((rank, F)) / np.sqrt(F)).astype(np.float32)
+    B_l = (rng.standard_normal((D, rank)) * 0.5).astype(np.float32)
+    return A_l, B_l
+
+
 def _single_rank_reference():
     x, (w_up, s_up, b_up), (w_dn, s_dn, b_dn) = _inputs()
     q, s = oracle.rot_q8_rows(x, D, block=BLOCK)
@@ -93,12 +101,29 @@ def _worker(rank, port, results):
         layer.accumulate_gated(h_local, X, g.upload(types[rank * rows:(rank + 1) * rows]), g.upload(gates), D)
         gated = X.numpy().copy()
         layer.close()
+        # a low-rank term on the row-parallel layer: T's partial sums pushed and reduced like the main product's
+        A_l, B_l = _adapter()
+        layer = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True, reduce="push",
+                                           lora=(A_l, B_l))
+        y_lora = [layer(h_local).numpy().copy() for _ in range(2)]
+        t_rows = layer.t_rows.numpy().copy()
+        layer.close()
+        layer = parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True, reduce="push",
+                                           scatter=True, lora=(A_l, B_l))
+        X = g.upload(x_stream[rank * rows:(rank + 1) * rows])
+        layer.accumulate_gated(h_local, X, g.upload(types[rank * rows:(rank + 1) * rows]), g.upload(gates), D)
+        gated_lora = X.numpy().copy()
+        layer.close()
+        with pytest.raises(ValueError):
+            parallel.RowParallelLinear(g, None, w_dn, s_dn, b_dn, M, block=BLOCK, swiglu_in=True, reduce="int32",
+                                       lora=(A_l, B_l))
         tok = parallel.TokenShardedLinear(g, None, parallel.ops.QWeight("q8", g.upload(w_up), g.upload(s_up), 2 * F, D,
                                                                          bias=g.upload(b_up)), M, block=BLOCK)
         h_tok = tok(g.upload(x[tok.m0:tok.m0 + tok.rows], "bf16"))
         results[rank] = dict(slices=up.slices, h_local=h_local.numpy().copy(), a8=down.a8.numpy().copy(),
                              sa=down.sa.numpy().copy(), y=y.numpy().copy(), y_rows=(down_rs.r0, y_rows.numpy().copy()), y_fast=y_fast.numpy().copy(),
-                             tok=(tok.m0, tok.rows, h_tok.numpy().copy()), pushed=pushed, gated=gated)
+                             tok=(tok.m0, tok.rows, h_tok.numpy().copy()), pushed=pushed, gated=gated, y_lora=y_lora,
+                             t_rows=t_rows, gated_lora=gated_lora)
     finally:
         dist.destroy_process_group()
 
@@ -144,6 +169,16 @@ def test_two_ranks_reproduce_one_rank_bit_for_bit():
         v = gemm_ref.epilogue_q8(acc, s2, _inputs()[2][1], _inputs()[2][2])
         want_x = gemm_ref.accumulate_gated(x_stream, v, gates, types)
         assert np.array_equal(r["gated"], want_x[r0:r0 + M // WORLD])
+        # low-rank term on the row-parallel layer: T of the rank's rows equals one GPU's T bit for bit (exact int32
+        # partial sums), and so does the output, the term joining after the bias as in the product's own epilogue
+        term = gemm_ref.low_rank_ref(*_adapter())
+        T = gemm_ref.lora_T(q2, s2, term)
+        assert np.array_equal(r["t_rows"], T[r0:r0 + M // WORLD])
+        y_term, v_term, _ = gemm_ref.gemm_q8(q2, _inputs()[2][0], s2, _inputs()[2][1], _inputs()[2][2], term, "bf16")
+        assert all(np.array_equal(o, y_term) for o in r["y_lora"])
+        assert not np.array_equal(y_term, y)  # the term is there
+        want_x = gemm_ref.accumulate_gated(x_stream, v_term, gates, types)
+        assert np.array_equal(r["gated_lora"], want_x[r0:r0 + M // WORLD])
         # token-sharded: rows of the full result
         m0, rows, h_tok = r["tok"]
         assert (m0, rows) == (rank * M // WORLD, M // WORLD) and np.array_equal(h_tok, h[m0:m0 + rows])
