@@ -42,11 +42,14 @@ NOMINAL_INT8_TOPS = 4500.0  # B200 dense int8, datasheet
 WINDOW_SECONDS = 1.0        # the repeated windows of the headline cover at least this much GPU time
 PEER_COPY_GBS = 770.0       # measured peer copy on this pool, per direction and GPU (nominal NVLink 5: 900)
 
-# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of
-# this benchmark's own step, averaged over the step's four product launches), keyed by config number. A figure can
-# only come from a profiler run, so it is recorded here with the capture it came from; configs without one print null.
+# DRAM traffic per launch of the dominant kernel: dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of this
+# benchmark's own step (ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum,gpu__time_duration.sum
+# --clock-control none -k regex:gemm_w8a8 -s 12 -c 4 python bench.py --config C --no-cpu --no-e2e --no-probe
+# --no-config4 --steps 2 --warmup 3), averaged over the step's four product launches, keyed by config number. Such a
+# figure can only come from a profiler run, so it is recorded here; configs without a capture print null.
 NCU_TRAFFIC_BYTES = {
-    1: 134.7e6,  # ncu --set full -k regex:gemm_w8a8 -s 4 -c 4, bench.py --config 1: 538.8 MB over the four launches
+    1: 139.9e6,   # 559.6 MB over the four launches (algorithmic 642.9 MB: part of the codes and outputs stays in L2)
+    3: 1648.4e6,  # 6593.8 MB over the four launches (algorithmic 3269.5 MB: W is re-read once per 32 MB band of A rows)
 }
 
 
@@ -511,8 +514,6 @@ def run_sharded(args, cfg, rank, world, gpu, timer, clocks, probe):
     e2e = None
     if not args.no_e2e:
         e2e, bufs = time_e2e(blk, timer, cfg.M, args.steps)
-        per_rank = [None] * world
-        dist.all_gather_object(per_rank, round(e2e["ms_per_step"], 4))
         e2e["h2d_bytes_per_step"] *= world   # whole job: every rank uploads its inputs and downloads its share
         e2e["d2h_bytes_per_step"] *= world
         e2e["per_rank"] = "bytes are the whole job's (all ranks); ms_per_step is the slowest rank's median window"

@@ -451,14 +451,15 @@ class TensorParallelBlock(HostStaged):
         self.gpu, self.cfg, self.layers, self.inputs = gpu, cfg, [], []
         self.rank, self.world = rank, world
         self.scratch = ops.Scratch(gpu)
-        for spec in cfg.layers:
+        for i, spec in enumerate(cfg.layers):
+            feeds_swiglu = i + 1 < len(cfg.layers) and cfg.layers[i + 1].swiglu_in  # its output is value | gate
             bias = torch.randn(spec.N, generator=gen, device=dev) * 0.01 if cfg.bias else None
             lora = workloads.lora_np(rng, cfg.lora_rank, spec.K, spec.N, cfg.block) if cfg.lora_rank else None
             if spec.parallel == "column" or all_column:
                 # a rank only needs its own rows: draw them directly (N / world rows)
                 n_local = spec.N // world
                 codes, scales = workloads.weight_torch(gen, n_local, spec.K, dev)
-                splits = [spec.N // 2, spec.N // 2] if (not all_column and spec.name == "w1w3") else None
+                splits = [spec.N // 2, spec.N // 2] if (not all_column and feeds_swiglu) else None
                 layer = ColumnParallelLinear(gpu, group, codes, scales, bias[:n_local].contiguous() if bias is not None else None,
                                              M, block=cfg.block, splits=splits, swiglu_in=spec.swiglu_in and not all_column,
                                              lora=lora, scratch=self.scratch, n_total=spec.N)

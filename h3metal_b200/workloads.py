@@ -60,6 +60,11 @@ CONFIGS = {
     2: Config("flux2-klein-4b-double-block", 4608,
               (Linear("qkv", 3072, 9216), Linear("out", 3072, 3072, parallel="row"), Linear("mlp_up", 3072, 9216),
                Linear("mlp_down", 9216, 3072, parallel="row")), lora_rank=32),
+    # the same block with the MLP as the reference's FLUX.2 runs it: fc1 3072 -> 18432 (value | gate), the SwiGLU
+    # quantiser, fc2 9216 -> 3072 (h3metal/flux2.py:142-144), timed beside the literal shape of configuration 2
+    5: Config("flux2-klein-4b-double-block-swiglu-mlp", 4608,
+              (Linear("qkv", 3072, 9216), Linear("out", 3072, 3072, parallel="row"), Linear("fc1", 3072, 18432),
+               Linear("fc2", 9216, 3072, swiglu_in=True, parallel="row")), lora_rank=32),
     3: Config("dit-33b-block-2048px", 17408, _block(6144, 16384)),
     4: Config("dit-33b-block-4096px-lora64", 66560, _block(6144, 16384), lora_rank=64),
 }

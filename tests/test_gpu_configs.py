@@ -91,6 +91,14 @@ def test_config2_flux2_block_with_lora(gpu, layer):
     _check_layer(gpu, cfg, cfg.layers[layer], cfg.M, 20 + layer, _rows(cfg.M, 48), cpu_weights=False)
 
 
+@pytest.mark.parametrize("layer", [2, 3])
+def test_config2_with_the_reference_swiglu_mlp(gpu, layer):
+    """The FLUX.2 block's MLP as the reference runs it (h3metal/flux2.py:142-144; shapes of tests/test_gemm.py:121-124):
+    fc1 3072 -> 18432, the SwiGLU quantiser, fc2 9216 -> 3072, with the rank-32 term."""
+    cfg = workloads.CONFIGS[5]
+    _check_layer(gpu, cfg, cfg.layers[layer], cfg.M, 50 + layer, _rows(cfg.M, 48), cpu_weights=False)
+
+
 @pytest.mark.parametrize("layer", range(4))
 def test_config3_33b_block(gpu, layer):
     cfg = workloads.CONFIGS[3]
