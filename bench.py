@@ -1,7 +1,7 @@
 """Benchmark of the W8A8 Hadamard-linear path on the linears of one DiT block: each linear is rotate+quantise followed
 by the int8 product with its epilogue. One "step" is one pass over the block's four linears on synthetic, seeded data.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 3]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 0..5] [--sweep]
 
 Default workload: the 33B-class block (M = 17408 tokens, hidden 6144: QKV 6144->18432, out 6144->6144,
 w1|w3 6144->32768, w2 16384->6144 fed by value*silu(gate)).
@@ -202,6 +202,22 @@ def workload_name(cfg) -> str:
             + (f", rank-{cfg.lora_rank} LoRA on every linear" if cfg.lora_rank else ""))
 
 
+def config_dict(cfg, world: int) -> dict:
+    """The line's `config`: what is measured, identical for both arms at a given number of GPUs."""
+    if world == 1:
+        how = "one GPU"
+    elif cfg.lora_rank:
+        how = f"every linear N-sharded (column-parallel) x{world}, LoRA rows follow the weight's; no exchange"
+    else:
+        how = (f"tp{world}: ONE block of M tokens; qkv and w1|w3 column-parallel, out and w2 row-parallel with the exact int32 "
+               f"reduction pushed over NVLink by the product kernel (reduce-scatter by peer stores, owner's sum + epilogue, "
+               f"all-gather by peer stores); whole-row scales by a pushed MAX exchange")
+    return {"workload": workload_name(cfg), "block": cfg.block, "parallelism": how,
+            "timing": "windows of --steps steps covering at least 1 s of GPU time, median window of the per-window maximum "
+                      "over ranks; barrier + synchronize around each window",
+            "l2": "per-step working set per GPU (weights plus activations and outputs) is several times the 126 MB L2"}
+
+
 def cpu_sample_text(cfg, rows: int) -> str:
     return (f"{rows} of {cfg.M} rows of every linear of the block per step (a row sample: the rate is per row and rows are "
             f"independent): the reference's NumPy arithmetic - fp32 rotation matmul, absmax int8, float64 BLAS product, "
@@ -220,7 +236,7 @@ def run_reference(args, cfg, rank, world):
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong" if args.gpus > 1 else "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": workload_name(cfg), "block": cfg.block},
+        "config": config_dict(cfg, world),
         "tops": value * cfg.ops / cfg.M / 1e12,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_sample_text(cfg, rows)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -394,6 +410,49 @@ def token_sharded_config4(gpu, args, timer, clocks, rank, world):
     return out
 
 
+def run_sweep(args):
+    """Config 4's stress sweep: K in {3072, 6144, 16384} x rotation block in {64, 128, 256} at M = 66560, N = 6144 -
+    rotate+quantise as achieved HBM GB/s, the product as TOP/s and int8 operations per clock and SM. One JSON line."""
+    import torch
+    from h3metal_b200 import ops
+    from h3metal_b200.gpu import Gpu
+    from h3metal_b200.linear import upload_weight
+    gpu = Gpu(device=int(os.environ.get("LOCAL_RANK", 0)))
+    dev = gpu.torch_device
+    timer = Timer(gpu, 1)
+    hbm, hbm_src, _ = hbm_peak()
+    M, N = 66560, 6144
+    out = {"workload": f"config 4 sweep: M={M}, N={N}", "hbm_peak_gbs": hbm, "hbm_peak_source": hbm_src, "rot_q8": {}, "gemm": {}}
+    with ClockSampler(gpu.device_index) as clocks:
+        probe = int8_peak_probe(gpu, clocks) if not args.no_probe else None
+        for K in (3072, 6144, 16384):
+            x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            X, a8, sa = gpu.wrap(x), gpu.empty((M, K), "i8"), gpu.empty((M,), "f32")
+            for block in (64, 128, 256):
+                fn = lambda: ops.rot_q8(gpu, X, a8, sa, M, K, block=block)  # noqa: E731
+                for _ in range(3):
+                    fn()
+                ms, _, _ = timer.windows(fn, args.steps, seconds=0.1)
+                gbs = M * (3 * K + 4) * args.steps / (ms * 1e-3) / 1e9
+                out["rot_q8"][f"K={K},block={block}"] = {"us": ms / args.steps * 1e3, "gbs": gbs, "frac_of_hbm_peak": gbs / hbm}
+            w = torch.randint(-127, 128, (N, K), device=dev, dtype=torch.int8)
+            wt = upload_weight(gpu, w, torch.rand(N, device=dev) * 1e-4 + 1e-4, torch.randn(N, device=dev) * 0.01)
+            C = gpu.empty((M, N), "bf16")
+            fn = lambda: ops.gemm(gpu, a8, wt, C, M, sa=sa, tile=(128, 32, 4))  # noqa: E731
+            for _ in range(3):
+                fn()
+            ms, _, spans = timer.windows(fn, max(2, args.steps // 4), seconds=0.5)
+            tops = 2.0 * M * N * K * max(2, args.steps // 4) / (ms * 1e-3) / 1e12
+            c = clocks.summary(spans[0][0], spans[-1][1])
+            out["gemm"][f"K={K}"] = {"us": ms / max(2, args.steps // 4) * 1e3, "tops": tops, "frac_of_nominal_4500": tops / NOMINAL_INT8_TOPS,
+                                     "frac_of_probe": tops / probe["peak_tops"] if probe else None, "sm_mhz": c["sm_mhz"],
+                                     "ops_per_clk_per_sm": tops * 1e12 / (gpu.sm_count * c["sm_mhz"] * 1e6) if c["sm_mhz"] else None}
+            del x, X, a8, w, wt, C
+            torch.cuda.empty_cache()
+        out["int8_probe"] = probe
+    return out
+
+
 def run_ours(args, cfg, rank, world):
     import torch
     import torch.distributed as dist
@@ -406,7 +465,6 @@ def run_ours(args, cfg, rank, world):
     gpu = Gpu(device=local)
     dev = gpu.torch_device
     timer = Timer(gpu, world)
-    wl = workload_name(cfg)
     with ClockSampler(local) as clocks:
         probe = int8_peak_probe(gpu, clocks) if (rank == 0 and not args.no_probe) else None
         if world > 1:
@@ -447,10 +505,8 @@ def run_ours(args, cfg, rank, world):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
-        "config": {"workload": wl, "block": cfg.block, "parallelism": "one GPU",
-                   "timing": f"{res['windows']} windows of {args.steps} steps, median window; barrier + synchronize around each",
-                   "l2": "per-step working set (weights plus activations and outputs) is several times the 126 MB L2"},
-        "tops": value / cfg.M * cfg.ops / 1e12,
+        "config": config_dict(cfg, 1),
+        "tops": value / cfg.M * cfg.ops / 1e12, "windows": res["windows"],
         "window_ms": res["window_ms"], "window_sm_mhz": res["window_clocks"],
         "roofline": res["roofline"], "roofline_rot_q8": res["roofline_rot_q8"], "norm_mod_q8": norm_extra,
         "int8_probe": probe, "e2e": e2e, "gpu_launches": res["launches_per_window"], "clocks": res["clocks"],
@@ -540,20 +596,12 @@ def run_sharded(args, cfg, rank, world, gpu, timer, clocks, probe):
     dist.barrier()
     if rank != 0:
         return None
-    if all_column:
-        how = f"every linear N-sharded (column-parallel) x{world}, LoRA rows follow the weight's; no exchange"
-    else:
-        how = (f"tp{world}: ONE block of M tokens; qkv and w1|w3 column-parallel, out and w2 row-parallel with the exact int32 "
-               f"reduction pushed over NVLink by the product kernel (reduce-scatter by peer stores, owner's sum + epilogue, "
-               f"all-gather by peer stores); whole-row scales by a pushed MAX exchange")
     return {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
-        "config": {"workload": workload_name(cfg), "block": cfg.block, "parallelism": how,
-                   "timing": f"{res['windows']} windows of {args.steps} steps, median window of the per-window maximum over ranks",
-                   "l2": "per-step working set per rank exceeds the 126 MB L2"},
-        "tops": value / cfg.M * cfg.ops / 1e12,
+        "config": config_dict(cfg, world),
+        "tops": value / cfg.M * cfg.ops / 1e12, "windows": res["windows"],
         "parity": {"ranks": world, "exact": True,
                    "what": "column-parallel -> swiglu quantiser -> row-parallel (push) chain equals each rank's own one-GPU result bit for bit"},
         "window_ms": res["window_ms"], "window_sm_mhz": res["window_clocks"],
@@ -576,6 +624,7 @@ def main():
     ap.add_argument("--no-probe", action="store_true", help="skip the int8 issue-rate probe")
     ap.add_argument("--no-config4", action="store_true", help="skip the token-sharded second object (config 4)")
     ap.add_argument("--no-variants", action="store_true", help="N > 1: skip the NCCL all-reduce run beside the pushed one")
+    ap.add_argument("--sweep", action="store_true", help="config 4's K x rotation-block stress sweep (one GPU) instead of a block")
     args = ap.parse_args()
 
     from h3metal_b200 import workloads
@@ -587,6 +636,10 @@ def main():
         line = run_reference(args, cfg, rank, world)
         if line is not None:
             print(json.dumps(line), flush=True)
+        return
+    if args.sweep:
+        if rank == 0:
+            print(json.dumps(run_sweep(args)), flush=True)
         return
 
     if world > 1:

@@ -542,10 +542,11 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
   // Staged stores (the epilogue writes 16-bit outputs to shared memory and TMA stores them) cost two of the six ring
   // stages. With a low-rank term - one accumulator pair, so the epilogue is not hidden behind the next tile - they are
   // what shortens the exposed part. Without one they still win where K is short (fewer K blocks per tile to hide the
-  // stores behind: +9 % at 3072 x 3072, +1 % at K = 6144) and lose 2-3 % to the shallower ring from K = 10240 on.
+  // stores behind: +9 % at 3072 x 3072, +1 % at K = 6144) and lose 2-3 % to the shallower ring from K = 10240 on -
+  // except for very tall products (M = 66560, K = 16384: +6 %), whose output no longer fits L2.
   const bool can_stage = pair && (c_dtype == H3B_BF16 || c_dtype == H3B_F16) && gate == nullptr && ctx->pair_stages_staged >= 2 &&
                          reinterpret_cast<uintptr_t>(C) % 16 == 0 && (c_stride * 2) % 16 == 0;
-  const bool staged = can_stage && (ctx->store_mode == 1 || (ctx->store_mode == 0 && (lora || K <= 8192)));
+  const bool staged = can_stage && (ctx->store_mode == 1 || (ctx->store_mode == 0 && (lora || K <= 8192 || M >= 32768)));
   const int bn = pair ? 128 : h3b_gemm_tile_n(ctx, N, lora);  // rows of W one CTA stages per K block
   const int stages = pair ? (staged ? ctx->pair_stages_staged : ctx->pair_stages)
                           : h3b::gemm_pick_stages(bn, lora ? R : 0, ctx->prop.sharedMemPerBlockOptin, push);
