@@ -529,9 +529,9 @@ def run_sharded(args, cfg, rank, world, gpu, timer, clocks, probe):
     dev = gpu.torch_device
 
     # ---- parity first: a timed configuration that was not checked proves nothing --------------------------------
-    verdict = parallel.check_sharded_chain(gpu, None, reduce="push")
+    check = parallel.check_sharded_chain(gpu, None, reduce="push")
     flags = [None] * world
-    dist.all_gather_object(flags, verdict)
+    dist.all_gather_object(flags, check)
     exact = all(f["exact"] for f in flags)
     if not exact:
         if rank == 0:

@@ -83,7 +83,7 @@ struct h3b_ctx {
   EncodeTiledFn encode = nullptr;
   std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
   int tile_n_override = 0, band_override = 0, pair_mode = 0, rot_threads = 0, rot_stages = 0, rot_chunk = 0;
-  int overlap = 0;  // programmatic dependent launch of the path's two main kernels (h3b_set_launch_overlap)
+  int overlap = 1;  // programmatic dependent launch of the path's main kernels (h3b_set_launch_overlap); on by default
   int pair_stages = 0, pair_clusters = 0;  // CTA-pair product: ring depth and resident clusters (0 = unavailable)
   int pair_stages_staged = 0;              // ring depth when 64 KB of shared memory stage the outputs for TMA stores
   int store_mode = 0;                      // staged (TMA) stores of the pair product: 0 automatic, 1 whenever possible, -1 never

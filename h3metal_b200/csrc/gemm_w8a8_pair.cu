@@ -116,6 +116,11 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
   cluster_sync_all();  // barriers of both CTAs exist before anyone signals across the pair
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
+  // everything above touched only the pair's shared and tensor memory; from here on global memory is read and written,
+  // which must wait for the kernel before this one in the stream (a no-op unless launched with programmatic stream
+  // serialization)
+  grid_dep_launch();
+  grid_dep_wait();
 
   if (warp == 0) {
     // ---------------------------------------------------------------------------------- TMA producer (both CTAs)
@@ -395,17 +400,30 @@ int gemm_pair_max_clusters(int stages) {
   return n < n_low ? n : n_low;
 }
 
+template <bool LORA, int EPI>
+cudaError_t launch_pair(const GemmLaunch &g, int stages, int clusters, size_t smem, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);  // the cluster shape (2, 1, 1) is part of the kernel's declaration
+  cfg.blockDim = dim3(64 + 32 * EPI);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g.overlap ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, gemm_w8a8_pair_kernel<LORA, EPI>, g, stages);
+}
+
 cudaError_t launch_gemm_w8a8_pair(const GemmLaunch &g, int stages, int clusters, cudaStream_t stream) {
   const size_t smem = gemm_pair_smem_bytes(stages, g.tma_store != 0);
   if (g.R > 0) {
     // one accumulator pair: the epilogue is exposed, so more warps share it (see g.epi_warps)
-    if (g.epi_warps == 16) gemm_w8a8_pair_kernel<true, 16><<<2 * clusters, 64 + 32 * 16, smem, stream>>>(g, stages);
-    else if (g.epi_warps == 8) gemm_w8a8_pair_kernel<true, 8><<<2 * clusters, 64 + 32 * 8, smem, stream>>>(g, stages);
-    else gemm_w8a8_pair_kernel<true, 4><<<2 * clusters, 64 + 32 * 4, smem, stream>>>(g, stages);
-  } else {
-    gemm_w8a8_pair_kernel<false, 4><<<2 * clusters, 64 + 32 * 4, smem, stream>>>(g, stages);
+    if (g.epi_warps == 16) return launch_pair<true, 16>(g, stages, clusters, smem, stream);
+    if (g.epi_warps == 8) return launch_pair<true, 8>(g, stages, clusters, smem, stream);
+    return launch_pair<true, 4>(g, stages, clusters, smem, stream);
   }
-  return cudaGetLastError();
+  return launch_pair<false, 4>(g, stages, clusters, smem, stream);
 }
 
 }  // namespace h3b

@@ -248,7 +248,7 @@ class Gpu:
             raise GpuError(_err())
 
     def set_launch_overlap(self, on: bool):
-        """Programmatic dependent launch of the path's kernels (off by default): a kernel's set-up overlaps the tail
+        """Programmatic dependent launch of the path's kernels (on by default): a kernel's set-up overlaps the tail
         of the kernel before it; every kernel still waits for its predecessor before touching global memory."""
         self._check(lib().h3b_set_launch_overlap(self.ctx, 1 if on else 0))
 

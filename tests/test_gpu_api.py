@@ -127,6 +127,6 @@ def test_launch_overlap_changes_no_result(gpu):
             gpu.wait()
             results.append((a2.numpy().copy(), y.numpy().copy()))
         finally:
-            gpu.set_launch_overlap(False)
+            gpu.set_launch_overlap(True)  # the library's default
     for codes, out in results[1:]:
         assert np.array_equal(codes, results[0][0]) and np.array_equal(out, results[0][1])
