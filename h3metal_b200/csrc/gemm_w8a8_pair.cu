@@ -14,16 +14,19 @@
 //   warp 1   leader only: issues the 256-row MMAs (kind::i8 into the int32 accumulator, kind::f16 for the low-rank
 //            term into a second, fp32 accumulator), releases a stage to both producers with a commit that arrives
 //            on both CTAs' empty barriers, and hands the accumulator to both epilogues the same way.
-//   warps 2-5 epilogue of this CTA's 128 rows (TMEM lanes of this SM); they free the accumulator stage by arriving
-//            on the LEADER's accumulator-empty barrier (the peer through the cluster address).
+//   warps 2.. epilogue of this CTA's 128 rows (TMEM lanes of this SM): four warps, one per lane quarter, or - with
+//            a low-rank term - sixteen, four per quarter with 64 columns each; they free the accumulator stage by
+//            arriving on the LEADER's accumulator-empty barrier (the peer through the cluster address).
 // Tensor memory is allocated for the pair (512 columns each): two 256-column int32 accumulators, so that the
 // epilogue of one tile overlaps the main loop of the next; with a low-rank term one int32 and one fp32 accumulator.
 //
-// Staged stores (16-bit outputs, no gate): an epilogue warp converts its 32 rows x 256 columns into its own 16 KB of
-// shared memory (four 128-byte-swizzled panels of 64 columns), gives the accumulator back as soon as the last
+// Staged stores (16-bit outputs, no gate): an epilogue warp converts its 32 rows of the tile into 128-byte-swizzled
+// panels of 64 columns in shared memory (16 KB per lane quarter), gives the accumulator back as soon as its last
 // tcgen05.ld has landed in registers, and lets TMA write the panels to global memory (cp.async.bulk.tensor, store
 // form, this GPU's memory only) while the tensor cores already work on the next tile. With ONE accumulator pair (the
 // low-rank case) this is what keeps the exposed part of the epilogue down to reading tensor memory.
+// Launched with programmatic stream serialization when the context asks for it: the set-up above the first global
+// access overlaps the previous kernel's tail.
 // All waits are bounded as in the single-CTA kernel. No load uses multicast.
 #include <cuda.h>
 
@@ -77,7 +80,7 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
   auto acc_empty_bar = [&](int i) { return bars + 144u + 8u * i; };
   volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(base_ptr + bars_off + 176);
   volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + bars_off + 180);
-  float *col_stage = reinterpret_cast<float *>(base_ptr + bars_off + kBarrierBytes);  // [4 warps][2][256]
+  float *col_stage = reinterpret_cast<float *>(base_ptr + bars_off + kBarrierBytes);  // [EPI warps][2][kWarpCols]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
