@@ -385,6 +385,23 @@ def time_e2e(blk, timer, tokens_per_step, steps):
             "per_rank": "bytes are this rank's; every rank moves its own inputs and outputs"}, (host_in, host_out)
 
 
+def time_without_low_rank(gpu, cfg, M, seed, steps, timer, ms_with, seconds=0.4):
+    """The same block with the same weights and inputs but no low-rank term on any linear, timed the same way: what
+    the term costs (its T product, the second accumulator's hand-over and the extra MMAs and loads)."""
+    import dataclasses
+    import torch
+    from h3metal_b200.linear import BlockLinears
+    blk = BlockLinears(gpu, dataclasses.replace(cfg, lora_rank=0), seed=seed, M=M)
+    for _ in range(3):
+        blk.step()
+    ms, ms_list, _ = timer.windows(blk.step, steps, seconds, at_least=3, at_most=9)
+    del blk
+    torch.cuda.empty_cache()
+    ms_without = ms / steps
+    return {"rank": cfg.lora_rank, "ms_per_step_with": ms_with, "ms_per_step_without": ms_without,
+            "overhead": ms_with / ms_without - 1.0, "windows": len(ms_list)}
+
+
 def token_sharded_config4(gpu, args, timer, clocks, rank, world):
     """The largest configuration at FIXED M, token-sharded: every rank runs the whole block (rank-64 LoRA on every
     linear) on M / world rows with replicated weights; no exchange. Returns the line's second object."""
@@ -407,6 +424,7 @@ def token_sharded_config4(gpu, args, timer, clocks, rank, world):
            "sm_mhz": clocks.summary(spans[0][0], spans[-1][1])["sm_mhz"]}
     del blk
     torch.cuda.empty_cache()
+    out["low_rank_term"] = time_without_low_rank(gpu, cfg, rows, 4321 + rank, steps, timer, ms / steps)
     return out
 
 
@@ -498,6 +516,7 @@ def run_ours(args, cfg, rank, world):
                       "frac_of_measured_hbm": norm_bytes / (norm_ms * 1e-3) / 1e9 / hbm}
         del blk, xres, X32
         torch.cuda.empty_cache()
+        low_rank = time_without_low_rank(gpu, cfg, cfg.M, 1234, args.steps, timer, res["ms_per_step"]) if cfg.lora_rank else None
         second = None if args.no_config4 or config_number(cfg) == 4 else token_sharded_config4(gpu, args, timer, clocks, rank, world)
         gpu.wait()
 
@@ -512,6 +531,8 @@ def run_ours(args, cfg, rank, world):
         "int8_probe": probe, "e2e": e2e, "gpu_launches": res["launches_per_window"], "clocks": res["clocks"],
         "config4_token_sharded": second,
     }
+    if low_rank:
+        line["low_rank_term"] = low_rank
     if not args.no_cpu:
         rows = args.cpu_rows or (1024 if cfg.ops < 4e12 else 256)
         cpu_value, _ = time_cpu(cfg, rows, 2, 1)

@@ -540,13 +540,16 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
                     (!lora || h3b_gemm_tile_n(ctx, N, 1) == 256) &&
                     (ctx->pair_mode == 1 || (ctx->pair_mode == 0 && pair_fits));
   // Staged stores (the epilogue writes 16-bit outputs to shared memory and TMA stores them) cost two of the six ring
-  // stages. With a low-rank term - one accumulator pair, so the epilogue is not hidden behind the next tile - they are
-  // what shortens the exposed part. Without one they still win where K is short (fewer K blocks per tile to hide the
-  // stores behind: +9 % at 3072 x 3072, +1 % at K = 6144) and lose 2-3 % to the shallower ring from K = 10240 on -
-  // except for very tall products (M = 66560, K = 16384: +6 %), whose output no longer fits L2.
+  // stages, about 1.5 k cycles of operand waits per tile, and shorten the epilogue by about 5 k cycles. The epilogue is
+  // hidden behind the next tile either way (with a low-rank term too: its int32 accumulator is handed back before any
+  // arithmetic), so they pay where only the last, exposed epilogue counts - launches of at most three tiles per pair
+  // with a short K (+3.5 % at 4096 x 3072 x 3072; -2.5 % on the 33B-class and Z-Image blocks) - and for very tall
+  // products, whose output no longer fits L2 (M = 66560: +1 %).
   const bool can_stage = pair && (c_dtype == H3B_BF16 || c_dtype == H3B_F16) && gate == nullptr && ctx->pair_stages_staged >= 2 &&
                          reinterpret_cast<uintptr_t>(C) % 16 == 0 && (c_stride * 2) % 16 == 0;
-  const bool staged = can_stage && (ctx->store_mode == 1 || (ctx->store_mode == 0 && (lora || K <= 8192 || M >= 32768)));
+  const long long pair_tiles = ((M + 255LL) / 256) * ((N + 255LL) / 256);
+  const bool few_tiles = pair && pair_tiles <= 3LL * ctx->pair_clusters && K <= 4096;
+  const bool staged = can_stage && (ctx->store_mode == 1 || (ctx->store_mode == 0 && (few_tiles || M >= 49152)));
   const int bn = pair ? 128 : h3b_gemm_tile_n(ctx, N, lora);  // rows of W one CTA stages per K block
   const int stages = pair ? (staged ? ctx->pair_stages_staged : ctx->pair_stages)
                           : h3b::gemm_pick_stages(bn, lora ? R : 0, ctx->prop.sharedMemPerBlockOptin, push);
@@ -569,7 +572,6 @@ static int gemm_enqueue(h3b_ctx *ctx, const int8_t *A, int64_t a_stride, const i
   // One accumulator pair leaves a low-rank product's epilogue exposed: sixteen warps (four per TMEM lane quarter, 64
   // columns each) read the accumulators out in a quarter of the time four would take. Measured on M = 66560,
   // 6144 -> 18432, rank 64, single launches: 6.11 / 5.95 / 5.25 ms with 4 / 8 / 16 warps against 4.7 ms without a term.
-  g.epi_warps = (pair && lora) ? 16 : 4;
   if (staged) {
     if (!(m = ctx->map2(cached_maps, &local, C, c_dtype, N, M, c_stride * 2, 64, 32, 128))) return -1;
     g.map_c = *m;

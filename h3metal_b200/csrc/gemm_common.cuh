@@ -151,6 +151,8 @@ __device__ __forceinline__ void dequant32(const GemmLaunch &g, const uint32_t (&
   }
 }
 
+__device__ __forceinline__ void store_values32(const GemmLaunch &g, const float (&v)[32], int m, int n, bool vec_ok);
+
 // Finishes 32 accumulator columns [n, n + 32) of row m: either the raw int32 values, or the dequantising
 // epilogue float(acc) * sa * sw (+ bias) (+ low) in the reference's operation order, converted to the output type
 // or, with a gate table, accumulated into the fp32 residual stream (the reference's epilogue 1,
@@ -177,6 +179,14 @@ __device__ __forceinline__ void finish_chunk(const GemmLaunch &g, const uint32_t
   }
   float v[32];
   dequant32(g, acc, low, has_low, sa_m, sw_s, bias_s, v);
+  store_values32(g, v, m, n, vec_ok);
+}
+
+// Stores 32 finished values of row m, columns [n, n + 32): converted to the output type, or accumulated into the fp32
+// residual stream with a gate table (the reference's epilogue 1).
+__device__ __forceinline__ void store_values32(const GemmLaunch &g, const float (&v)[32], int m, int n, bool vec_ok) {
+  const int n_valid = g.N - n;
+  if (m >= g.M || n_valid <= 0) return;
   const size_t off = static_cast<size_t>(m) * g.c_stride + n;
   if (g.gate != nullptr) {
     // gated-residual epilogue: X[m][n] += gate[type[m]][n] * v, X the fp32 residual stream (one multiply, one add)

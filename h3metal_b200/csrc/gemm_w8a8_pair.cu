@@ -9,22 +9,25 @@
 // Roles per CTA (rank 0 = leader, rank 1 = peer):
 //   warp 0   TMA producer: own A rows and own half of W into this CTA's ring; completion bytes of BOTH CTAs are
 //            counted on the LEADER's full barrier (the leader's producer arms it with the pair's total). With a
-//            low-rank term the tile's T rows and this CTA's half of the B' rows travel through the same ring ahead
-//            of the K blocks, 64 ranks per stage.
-//   warp 1   leader only: issues the 256-row MMAs (kind::i8 into the int32 accumulator, kind::f16 for the low-rank
-//            term into a second, fp32 accumulator), releases a stage to both producers with a commit that arrives
-//            on both CTAs' empty barriers, and hands the accumulator to both epilogues the same way.
+//            low-rank term the tile's T rows and this CTA's half of the B' rows travel through the same ring after
+//            the K blocks, 64 ranks per stage.
+//   warp 1   leader only: issues the 256-row MMAs (kind::i8 into the int32 accumulator, then kind::f16 for the
+//            low-rank term into a second, fp32 accumulator), releases a stage to both producers with a commit that
+//            arrives on both CTAs' empty barriers, and hands the accumulators to both epilogues the same way.
 //   warps 2.. epilogue of this CTA's 128 rows (TMEM lanes of this SM): four warps, one per lane quarter, or - with
 //            a low-rank term - sixteen, four per quarter with 64 columns each; they free the accumulator stage by
 //            arriving on the LEADER's accumulator-empty barrier (the peer through the cluster address).
 // Tensor memory is allocated for the pair (512 columns each): two 256-column int32 accumulators, so that the
-// epilogue of one tile overlaps the main loop of the next; with a low-rank term one int32 and one fp32 accumulator.
+// epilogue of one tile overlaps the main loop of the next. With a low-rank term there is room for one int32 and one
+// fp32 accumulator only, and the hand-over is split in two: an epilogue warp copies its int32 values to registers
+// and frees that accumulator before any arithmetic (the next tile's main loop starts after one TMEM read), and
+// gives the fp32 accumulator back on a barrier of its own, which the leader waits for only before the next tile's
+// LAST instructions - the term's.
 //
 // Staged stores (16-bit outputs, no gate): an epilogue warp converts its 32 rows of the tile into 128-byte-swizzled
 // panels of 64 columns in shared memory (16 KB per lane quarter), gives the accumulator back as soon as its last
 // tcgen05.ld has landed in registers, and lets TMA write the panels to global memory (cp.async.bulk.tensor, store
-// form, this GPU's memory only) while the tensor cores already work on the next tile. With ONE accumulator pair (the
-// low-rank case) this is what keeps the exposed part of the epilogue down to reading tensor memory.
+// form, this GPU's memory only) while the tensor cores already work on the next tile.
 // Launched with programmatic stream serialization when the context asks for it: the set-up above the first global
 // access overlaps the previous kernel's tail.
 // All waits are bounded as in the single-CTA kernel. No load uses multicast.
@@ -62,7 +65,7 @@ __device__ __forceinline__ void stage_out32(uint8_t *warp_buf, int c, int lane, 
 template <bool LORA, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * EPI, 1)
 gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
-  static_assert(EPI == 4 || EPI == 8 || EPI == 16, "one, two or four epilogue warps per TMEM lane quarter");
+  static_assert((!LORA && EPI == 4) || (LORA && EPI == 16), "four epilogue warps, or sixteen with a low-rank term");
   constexpr int kAccStages = LORA ? 1 : 2;
   constexpr int kWarpCols = kPairBN / (EPI / 4);  // columns of the tile one epilogue warp finishes
   constexpr int kWarpChunks = kWarpCols / 32;
@@ -78,6 +81,7 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
   auto empty_bar = [&](int i) { return bars + 64u + 8u * i; };
   auto acc_full_bar = [&](int i) { return bars + 128u + 8u * i; };
   auto acc_empty_bar = [&](int i) { return bars + 144u + 8u * i; };
+  const uint32_t low_empty_bar = bars + 160u;  // low-rank accumulator free (LORA): its own hand-over, see the epilogue
   volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(base_ptr + bars_off + 176);
   volatile int *cta_abort = reinterpret_cast<volatile int *>(base_ptr + bars_off + 180);
   float *col_stage = reinterpret_cast<float *>(base_ptr + bars_off + kBarrierBytes);  // [EPI warps][2][kWarpCols]
@@ -108,6 +112,7 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
       mbar_init(acc_full_bar(i), 1);
       mbar_init(acc_empty_bar(i), 2 * EPI);  // the epilogue warps of both CTAs of the pair
     }
+    mbar_init(low_empty_bar, 2 * EPI);
     *cta_abort = 0;
     fence_barrier_init();
   }
@@ -137,7 +142,20 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
         const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, g.band);
         const int m0 = tc.m_blk * 256 + static_cast<int>(rank) * 128;
         const int n0 = tc.n_blk * kPairBN + static_cast<int>(rank) * 128;
-        if (LORA) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const uint32_t s = pos.s;
+          ok = mbar_wait(empty_bar(s), pos.ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
+          if (!ok) break;
+          if (leader) mbar_arrive_expect_tx(full_bar(s), 2u * kPairStage);
+          const uint32_t leader_full = leader_full0 + 8u * s;
+          const uint32_t dst = base + s * kPairStage;
+          tma_load_2d_pair(dst, &g.map_a, leader_full, kb * kBKBytes, m0);
+          tma_load_2d_pair(dst + kABytes, &g.map_w, leader_full, kb * kBKBytes, n0);
+          pos.advance(stages);
+          filled += filled < static_cast<uint32_t>(stages);
+        }
+        if (!ok) break;
+        if (LORA) {  // the term's operands follow the tile's K blocks (its MMAs are the tile's last)
           for (int j = 0; ok && j < lora_blocks; ++j) {
             const uint32_t s = pos.s;
             ok = mbar_wait(empty_bar(s), pos.ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
@@ -153,19 +171,6 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
             pos.advance(stages);
             filled += filled < static_cast<uint32_t>(stages);
           }
-          if (!ok) break;
-        }
-        for (int kb = 0; kb < num_kb; ++kb) {
-          const uint32_t s = pos.s;
-          ok = mbar_wait(empty_bar(s), pos.ph ^ 1u, cta_abort, g.status, kStatusProducerTimeout);
-          if (!ok) break;
-          if (leader) mbar_arrive_expect_tx(full_bar(s), 2u * kPairStage);
-          const uint32_t leader_full = leader_full0 + 8u * s;
-          const uint32_t dst = base + s * kPairStage;
-          tma_load_2d_pair(dst, &g.map_a, leader_full, kb * kBKBytes, m0);
-          tma_load_2d_pair(dst + kABytes, &g.map_w, leader_full, kb * kBKBytes, n0);
-          pos.advance(stages);
-          filled += filled < static_cast<uint32_t>(stages);
         }
       }
       if (*cta_abort && leader) {
@@ -195,13 +200,36 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_acc = tmem_base + as * kPairBN;
-        if (LORA) {
+        // the tile's rank range is needed after the main loop only: its two loads are issued here, off the critical path
+        int k0 = 0, k1 = g.R;
+        if (LORA && g.ranges != nullptr) {
           const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, g.band);
-          int k0 = 0, k1 = g.R;
-          if (g.ranges != nullptr) {
-            k0 = g.ranges[2 * tc.n_blk];
-            k1 = g.ranges[2 * tc.n_blk + 1];
-          }
+          k0 = ld_nc_s32_here(g.ranges + 2 * tc.n_blk);
+          k1 = ld_nc_s32_here(g.ranges + 2 * tc.n_blk + 1);
+        }
+        uint32_t accumulate = 0;  // the tile's first instruction overwrites the accumulator
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const uint32_t s = pos.s;
+          ok = mbar_wait(full_bar(s), pos.ph, cta_abort, g.status, kStatusMmaTimeout);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t ad = ad0 + static_cast<uint64_t>(s * (kPairStage >> 4));
+          const uint64_t bd = bd0 + static_cast<uint64_t>(s * (kPairStage >> 4));
+          umma_i8_pair(d_acc, ad, bd, idesc, accumulate);
+          accumulate = 1;
+#pragma unroll
+          for (int k = 1; k < kBKBytes / 32; ++k) umma_i8_pair(d_acc, ad + 2u * k, bd + 2u * k, idesc, 1u);
+          umma_commit_pair(empty_bar(s), 3);  // both producers may refill this stage once the MMAs have read it
+          pos.advance(stages);
+        }
+        if (!ok) break;
+        if (LORA) {
+          // The low-rank MMAs are the tile's last: the fp32 accumulator they write is handed back by the epilogue of
+          // the tile before on a barrier of its own, long after that epilogue has freed the int32 accumulator - so the
+          // main loop above already ran while the epilogue was still finishing.
+          ok = mbar_wait(low_empty_bar, aph ^ 1u, cta_abort, g.status, kStatusMmaTimeout);
+          if (!ok) break;
+          tc_fence_after_sync();
           const uint32_t d_low = tmem_base + kLowBase;
           for (int j = 0; ok && j < lora_blocks; ++j) {
             const uint32_t s = pos.s;
@@ -222,22 +250,6 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
           }
           if (!ok) break;
         }
-        uint32_t accumulate = 0;  // the tile's first instruction overwrites the accumulator
-        for (int kb = 0; kb < num_kb; ++kb) {
-          const uint32_t s = pos.s;
-          ok = mbar_wait(full_bar(s), pos.ph, cta_abort, g.status, kStatusMmaTimeout);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint64_t ad = ad0 + static_cast<uint64_t>(s * (kPairStage >> 4));
-          const uint64_t bd = bd0 + static_cast<uint64_t>(s * (kPairStage >> 4));
-          umma_i8_pair(d_acc, ad, bd, idesc, accumulate);
-          accumulate = 1;
-#pragma unroll
-          for (int k = 1; k < kBKBytes / 32; ++k) umma_i8_pair(d_acc, ad + 2u * k, bd + 2u * k, idesc, 1u);
-          umma_commit_pair(empty_bar(s), 3);  // both producers may refill this stage once the MMAs have read it
-          pos.advance(stages);
-        }
-        if (!ok) break;
         umma_commit_pair(acc_full_bar(as), 3);  // both epilogues
       }
     }
@@ -255,6 +267,7 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
     uint8_t *out_buf = base_ptr + out_off + quarter * kOutWarp;  // this warp's staging (staged stores only)
     const uint32_t out_addr = base + out_off + quarter * kOutWarp;
     const uint32_t leader_acc_empty0 = map_to_cta(acc_empty_bar(0), 0);
+    const uint32_t leader_low_empty = map_to_cta(low_empty_bar, 0);
     uint32_t at = 0;
     bool ok = true;
     for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++at) {
@@ -285,49 +298,85 @@ gemm_w8a8_pair_kernel(const __grid_constant__ GemmLaunch g, const int stages) {
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * kPairBN;
       const uint32_t t_low = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kLowBase;
-      auto fetch = [&](int c, uint32_t (&acc)[32], uint32_t (&low)[32]) {
-        tmem_ld_32x32b_x32(t_acc + c * 32, acc);
-        if (LORA && has_low) tmem_ld_32x32b_x32(t_low + c * 32, low);
-      };
       auto release = [&]() {  // every value of the accumulator is in registers: the leader may overwrite it
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8u * as);
       };
-      auto finish = [&](const uint32_t (&acc)[32], const uint32_t (&low)[32], int c) {  // c: chunk of the tile
-        const float *sw_c = sw_s + (c - c_begin) * 32, *bias_c = bias_s + (c - c_begin) * 32;
-        if (staged) {
-          float v[32];
-          dequant32(g, acc, low, LORA && has_low, sa_m, sw_c, bias_c, v);
-          if (g.c_dtype == kDtypeBf16) stage_out32<__nv_bfloat16>(out_buf, c, lane, v);
-          else stage_out32<__half>(out_buf, c, lane, v);
-        } else {
-          finish_chunk(g, acc, low, LORA && has_low, m, n0 + c * 32, sa_m, sw_c, bias_c, vec_ok);
+      if constexpr (LORA) {
+        // Split hand-over. The warp reads both of its 32-column chunks of the int32 accumulator into registers and frees
+        // that accumulator at once: the leader starts the next tile's main loop while the arithmetic below runs. The
+        // low-rank accumulator is written by the LAST instructions of a tile, so it is handed back on a barrier of its
+        // own after it has been read, long before the leader needs it. The exposed part of the epilogue is one TMEM
+        // read; the values are identical to the joint order (the term is the last addend either way).
+        uint32_t a0[32], a1[32];
+        const uint32_t no_low[32] = {};
+        tmem_ld_32x32b_x32(t_acc + c_begin * 32, a0);
+        tmem_ld_32x32b_x32(t_acc + (c_begin + 1) * 32, a1);
+        tmem_ld_wait();
+        release();
+        auto put = [&](const float (&v)[32], int c) {
+          if (staged) {
+            if (g.c_dtype == kDtypeBf16) stage_out32<__nv_bfloat16>(out_buf, c, lane, v);
+            else stage_out32<__half>(out_buf, c, lane, v);
+          } else {
+            store_values32(g, v, m, n0 + c * 32, vec_ok);
+          }
+        };
+        // the term's 64 columns come in pieces of 16: with both int32 chunks held, registers are the limit
+        auto add_low = [&](float (&v)[32], int c, int half) {
+          uint32_t low[16];
+          tmem_ld_32x32b_x16(t_low + c * 32 + half * 16, low);
+          tmem_ld_wait();
+          if (c == c_begin + 1 && half == 1) {  // the warp's last values of the low-rank accumulator are in registers
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_low_empty);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[half * 16 + j] = __fadd_rn(v[half * 16 + j], __uint_as_float(low[j]));
+        };
+        float v[32];
+        dequant32(g, a0, no_low, false, sa_m, sw_s, bias_s, v);
+        if (has_low) {
+          add_low(v, c_begin, 0);
+          add_low(v, c_begin, 1);
         }
-      };
-      if constexpr (EPI == 4) {
+        put(v, c_begin);
+        dequant32(g, a1, no_low, false, sa_m, sw_s + 32, bias_s + 32, v);
+        if (has_low) {
+          add_low(v, c_begin + 1, 0);
+          add_low(v, c_begin + 1, 1);
+        } else {
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(leader_low_empty);  // nothing to read: hand it back unread
+        }
+        put(v, c_begin + 1);
+      } else {
         // two register sets: the TMEM loads of the next 32 columns are in flight while this chunk is finished
-        uint32_t acc_a[32], low_a[32], acc_b[32], low_b[32];
-        fetch(c_begin, acc_a, low_a);
+        uint32_t acc_a[32], acc_b[32];
+        const uint32_t no_low[32] = {};
+        auto finish = [&](const uint32_t (&acc)[32], int c) {  // c: chunk of the tile
+          const float *sw_c = sw_s + (c - c_begin) * 32, *bias_c = bias_s + (c - c_begin) * 32;
+          if (staged) {
+            float v[32];
+            dequant32(g, acc, no_low, false, sa_m, sw_c, bias_c, v);
+            if (g.c_dtype == kDtypeBf16) stage_out32<__nv_bfloat16>(out_buf, c, lane, v);
+            else stage_out32<__half>(out_buf, c, lane, v);
+          } else {
+            finish_chunk(g, acc, no_low, false, m, n0 + c * 32, sa_m, sw_c, bias_c, vec_ok);
+          }
+        };
+        tmem_ld_32x32b_x32(t_acc + c_begin * 32, acc_a);
 #pragma unroll 1
         for (int c = c_begin; c < c_begin + kWarpChunks; c += 2) {
           tmem_ld_wait();
-          fetch(c + 1, acc_b, low_b);
-          finish(acc_a, low_a, c);
+          tmem_ld_32x32b_x32(t_acc + (c + 1) * 32, acc_b);
+          finish(acc_a, c);
           tmem_ld_wait();
-          if (c + 2 < c_begin + kWarpChunks) fetch(c + 2, acc_a, low_a);
+          if (c + 2 < c_begin + kWarpChunks) tmem_ld_32x32b_x32(t_acc + (c + 2) * 32, acc_a);
           else release();  // the warp's last values have left tensor memory
-          finish(acc_b, low_b, c + 1);
-        }
-      } else {
-        // several warps per scheduler hide one another's TMEM latency; one register set keeps them within the budget
-        uint32_t acc_a[32], low_a[32];
-#pragma unroll 1
-        for (int c = c_begin; c < c_begin + kWarpChunks; ++c) {
-          fetch(c, acc_a, low_a);
-          tmem_ld_wait();
-          if (c + 1 == c_begin + kWarpChunks) release();  // the warp's last values have left tensor memory
-          finish(acc_a, low_a, c);
+          finish(acc_b, c + 1);
         }
       }
       if (staged) {
@@ -380,7 +429,7 @@ cudaError_t gemm_pair_configure() {
   if ((e = cudaFuncSetAttribute(gemm_w8a8_pair_kernel<L, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448)) != \
       cudaSuccess)                                                                                                     \
     return e;
-  H3B_PAIR_CFG(false, 4) H3B_PAIR_CFG(true, 4) H3B_PAIR_CFG(true, 8) H3B_PAIR_CFG(true, 16)
+  H3B_PAIR_CFG(false, 4) H3B_PAIR_CFG(true, 16)
 #undef H3B_PAIR_CFG
   return cudaSuccess;
 }
@@ -420,12 +469,8 @@ cudaError_t launch_pair(const GemmLaunch &g, int stages, int clusters, size_t sm
 
 cudaError_t launch_gemm_w8a8_pair(const GemmLaunch &g, int stages, int clusters, cudaStream_t stream) {
   const size_t smem = gemm_pair_smem_bytes(stages, g.tma_store != 0);
-  if (g.R > 0) {
-    // one accumulator pair: the epilogue is exposed, so more warps share it (see g.epi_warps)
-    if (g.epi_warps == 16) return launch_pair<true, 16>(g, stages, clusters, smem, stream);
-    if (g.epi_warps == 8) return launch_pair<true, 8>(g, stages, clusters, smem, stream);
-    return launch_pair<true, 4>(g, stages, clusters, smem, stream);
-  }
+  // with a low-rank term: one int32 accumulator, so its hand-over is exposed and sixteen warps share the epilogue
+  if (g.R > 0) return launch_pair<true, 16>(g, stages, clusters, smem, stream);
   return launch_pair<false, 4>(g, stages, clusters, smem, stream);
 }
 

@@ -143,7 +143,6 @@ struct GemmLaunch {
   void *peer_c[kMaxPeers];
   int peer_rows;
   int overlap;         // host side: launch with programmatic stream serialization (prologue overlaps the previous kernel's tail)
-  int epi_warps;       // CTA pairs with a low-rank term: epilogue warps per CTA (4, 8 or 16)
   int tma_store;       // CTA pairs: the epilogue stages 16-bit outputs in shared memory and TMA stores them (map_c)
 };
 

@@ -473,7 +473,7 @@ class Gpu:
 
     def set_store_mode(self, mode: int = 0):
         """How CTA pairs write 16-bit outputs: 1 staged through shared memory and TMA stores whenever possible,
-        -1 direct stores from registers, 0 automatic (staged with a low-rank term or K <= 8192)."""
+        -1 direct stores from registers, 0 automatic (staged for short launches with K <= 4096 and for M >= 49152)."""
         self._check(lib().h3b_gemm_set_store_mode(self.ctx, mode))
 
     def set_policy(self, tile_n: int = 0, band: int = 0, rot_threads: int = 0, rot_stages: int = 0, pair: int = 0,

@@ -277,8 +277,9 @@ H3B_API int h3b_gemm_set_policy(h3b_ctx *ctx, int tile_n, int band, int pair);
 /* How the CTA-pair product writes 16-bit outputs: 1 = staged - the epilogue converts a tile into shared memory,
  * frees the accumulator at once and TMA stores the tile while the next one is being multiplied - whenever the output
  * is bf16 / f16, not gated and 16-byte aligned; -1 = always with direct stores from registers; 0 = automatic
- * (staged for products with a low-rank term, whose single accumulator pair leaves the epilogue exposed, and for
- * products of K <= 8192, which have few K blocks per tile to hide direct stores behind, or of M >= 32768).
+ * (staged for launches of at most three tiles per CTA pair with K <= 4096, where the last, exposed epilogue counts,
+ * and for very tall products, M >= 49152, whose output no longer fits L2; everything else gains more from the two
+ * ring stages that staging costs).
  * No reference counterpart. Returns 0. */
 H3B_API int h3b_gemm_set_store_mode(h3b_ctx *ctx, int mode);
 /* Tuning of the rotate+quantise kernel. tma_stages: rows a CTA keeps in flight in shared memory (1..4), 0 =
