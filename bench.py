@@ -49,7 +49,7 @@ PEER_COPY_GBS = 770.0       # measured peer copy on this pool, per direction and
 # figure can only come from a profiler run, so it is recorded here; configs without a capture print null.
 NCU_TRAFFIC_BYTES = {
     1: 139.9e6,   # 559.6 MB over the four launches (algorithmic 642.9 MB: part of the codes and outputs stays in L2)
-    3: 1648.4e6,  # 6593.8 MB over the four launches (algorithmic 3269.5 MB: W is re-read once per 32 MB band of A rows)
+    3: 1790.4e6,  # 7161.6 MB over the four launches (algorithmic 3269.5 MB: W is re-read once per 32 MB band of A rows)
 }
 
 
