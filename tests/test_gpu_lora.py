@@ -89,7 +89,7 @@ def test_dense_adapters(gpu, rank, N, K, tile_n):
 
 
 @pytest.mark.parametrize("out_dtype,store", [("f32", 0), ("bf16", -1), ("bf16", 1), ("f16", 1)])
-@pytest.mark.parametrize("rank", [32, 64, 128])
+@pytest.mark.parametrize("rank", [32, 64, 96, 128])
 def test_low_rank_on_cta_pairs(gpu, out_dtype, store, rank):
     """The term inside the CTA-pair product (256 x 256 tiles, one accumulator pair), with stores from registers and
     with the epilogue staged through shared memory; several tiles per pair, ragged M, against the oracle and against
@@ -102,6 +102,22 @@ def test_low_rank_on_cta_pairs(gpu, out_dtype, store, rank):
     assert rel_fro(r["got_f"][:M], want[:M]) <= (1e-5 if out_dtype == "f32" else 1e-3)
     single = _run(gpu, np.random.default_rng(4), M, N, K, A_l, B_l, out_dtype, pair=-1)
     assert rel_fro(r["got_f"][:M], single["got_f"][:M]) <= 1e-5
+    assert not r["got"][ops.pad_rows(M):].any()
+
+
+@pytest.mark.parametrize("rank,store", [(32, -1), (96, -1), (96, 1)])
+def test_low_rank_over_several_tiles_per_pair(gpu, rank, store):
+    """9 x 20 = 180 tiles of 256 x 256 on at most 74 CTA pairs: every pair finishes two or three tiles, so both
+    accumulators are handed back and taken again (the int32 one before any arithmetic, the low-rank one on its own
+    barrier) with the next tile's main loop already running. Ragged M; rank 96 = one full and one half operand stage."""
+    M, N, K = 2300, 5120, 768
+    A_l = (np.random.default_rng(rank).standard_normal((rank, K)) / np.sqrt(K)).astype(np.float32)
+    B_l = (np.random.default_rng(rank + 1).standard_normal((N, rank)) * 0.5).astype(np.float32)
+    r = _run(gpu, np.random.default_rng(5), M, N, K, A_l, B_l, "bf16", pair=1, store=store)
+    want = oracle.bf16_bits_to_f32(r["stored"])
+    assert rel_fro(r["got_f"][:M], want[:M]) <= 1e-3
+    single = _run(gpu, np.random.default_rng(5), M, N, K, A_l, B_l, "bf16", pair=-1)
+    assert np.array_equal(r["got"][:M], single["got"][:M]) or rel_fro(r["got_f"][:M], single["got_f"][:M]) <= 1e-5
     assert not r["got"][ops.pad_rows(M):].any()
 
 
